@@ -25,6 +25,7 @@ typedef void* spd_stream_t; /* cudaStream_t */
 /* element types of activations / weights / KV pool */
 #define SPD_BF16 0
 #define SPD_F16 1
+#define SPD_F32 2 /* the operators of the "32-bit capable ops" section only */
 
 /* argument-check error codes (CUDA errors are returned as positive cudaError_t values) */
 #define SPD_E_BADARG (-1)   /* null pointer, non-positive size, bad enum */
@@ -338,6 +339,81 @@ int spd_attn_mla(void* out, const void* q, const void* kv_pool, const int32_t* r
                  int kv_lora_rank, int rope_dim, int64_t q_stride, int64_t out_stride,
                  int64_t req_to_token_stride, float sm_scale, int dtype, void* workspace,
                  int64_t workspace_bytes, int sm_budget, spd_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * 32-bit capable ops — the operators of the hybrid (windowed attention + retention + MoE) model
+ * family.  dtype is SPD_BF16 / SPD_F16 / SPD_F32 (activations, weights and KV pool alike); softmax,
+ * norms, routing, the residual stream and recurrent state are fp32 whatever the dtype.  The
+ * reference has no such models; the calling conventions follow the ops above.
+ * ------------------------------------------------------------------------------------------- */
+/* x[r, :] += a[r, :] (+ b[r, :])   (x fp32 residual stream, a / b nullable, dtype elements);
+ * out[r, :] = x[r, :] / sqrt(mean(x[r, :]^2) + eps) * (weight_offset + w[:])   (out nullable) */
+int spd_residual_rmsnorm(void* out, float* x, const void* a, const void* b, const void* w, int64_t rows,
+                         int64_t dim, float eps, float weight_offset, int dtype, spd_stream_t stream);
+/* x[r, :] = table[idx[r], :] as fp32 (embedding lookup into the fp32 residual stream) */
+int spd_embed_f32(float* x, const void* table, const int64_t* idx, int64_t rows, int64_t dim,
+                  int64_t table_rows, int dtype, spd_stream_t stream);
+/* out[r, i] = act(x[r, i]) * x[r, inter + i]; act 0 = SiLU, 1 = tanh-form GELU.  x [rows, 2 inter] */
+int spd_act_and_mul(void* out, const void* x, int64_t rows, int64_t inter, int act, int dtype,
+                    spd_stream_t stream);
+/* out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * silu(g[t, h, :]);  o fp32 [tokens, heads *
+ * vdim] contiguous, g dtype with row stride g_stride, out dtype contiguous */
+int spd_headnorm_gate(void* out, const float* o, const void* g, int64_t tokens, int heads, int vdim,
+                      int64_t g_stride, float eps, int dtype, spd_stream_t stream);
+/* C = A W^T on the CUDA cores with fp32 accumulation in ascending-k order (any M, N, K; any dtype).
+ * tile_group != NULL: rows of A are grouped in 128-row tiles (spd_moe_align) and rows
+ * [g * w_group_rows, +N) of W multiply the tiles of group g = tile_group[row / 128] (< 0: skipped). */
+int spd_linear_simt(void* C, const void* A, const void* W, int64_t M, int64_t N, int64_t K, int64_t lda,
+                    int64_t ldw, int64_t ldc, const int32_t* tile_group, int64_t w_group_rows, int dtype,
+                    int out_f32, spd_stream_t stream);
+/* Routing from fp32 logits (row stride ld): score = softmax (score_func 0) or sigmoid (1) of the logits,
+ * the top_k largest scores are chosen (ties: smaller expert id), weights = score (renormalised over the
+ * chosen ones if renormalize) x scale. */
+int spd_moe_route_scores(int32_t* topk_ids, float* topk_w, const float* logits, int64_t ld, int64_t tokens,
+                         int num_experts, int top_k, int score_func, int renormalize, float scale,
+                         spd_stream_t stream);
+/* xs[r, :] = w(r) * x[row_token[r], :] with w(r) the routing weight of the entry sorted to row r (1 if
+ * topk_w == NULL); zeros for padding rows — experts that weight their INPUT */
+int spd_moe_gather_scaled(void* xs, const void* x, const int32_t* row_token, const int32_t* inv_pos,
+                          const float* topk_w, int64_t rows, int top_k, int64_t dim, int64_t x_stride,
+                          int dtype, spd_stream_t stream);
+/* out[t, :] = sum_j (topk_w ? topk_w[t, j] : 1) * y[inv_pos[t * top_k + j], :]
+ *           + (shared ? (shared_gate ? sigmoid(shared_gate[t * gate_stride]) : 1) * shared[t, :] : 0) */
+int spd_moe_combine_gated(void* out, const void* y, const int32_t* inv_pos, const float* topk_w,
+                          const void* shared, const float* shared_gate, int64_t gate_stride, int64_t tokens,
+                          int top_k, int64_t dim, int dtype, spd_stream_t stream);
+/* k_pool[loc[t]] = k[t], v_pool[loc[t]] = v[t] with different row sizes for keys and values */
+int spd_kv_store(const void* k, const void* v, void* k_pool, void* v_pool, const int64_t* loc,
+                 int64_t tokens, int64_t k_row_elems, int64_t v_row_elems, int64_t k_stride,
+                 int64_t v_stride, int dtype, spd_stream_t stream);
+/* Softmax attention over the paged pool with the options of the hybrid family, decode (seq_lens !=
+ * NULL: one query per request at position seq_lens[b] - 1) or ragged extend (query j of request r is row
+ * extend_start_loc[r] + j of q, position prefix_lens[r] + j).  Query i sees keys j with 0 <= i - j <
+ * window (window <= 0: all j <= i).  score = (q . k) * sm_scale * temp(i) - slopes[h] * (i - j) with
+ * temp(i) = 1 + qtemp_coef * ln(floor((i + 1) / qtemp_every) + 1) (qtemp_every <= 0: 1); slopes nullable.
+ * sinks != NULL: exp(sinks[h]) joins the softmax denominator.  key size head_dim, value size v_dim;
+ * k_pool [slots, kv_heads, head_dim], v_pool [slots, kv_heads, v_dim]; out [tokens, heads * v_dim]. */
+int spd_attn_general(void* out, const void* q, const void* k_pool, const void* v_pool,
+                     const int32_t* req_to_token, const int64_t* req_pool_indices, const int64_t* seq_lens,
+                     const int32_t* prefix_lens, const int32_t* extend_lens, const int32_t* extend_start_loc,
+                     int64_t batch, int64_t total_tokens, int num_q_heads, int num_kv_heads, int head_dim,
+                     int v_dim, int64_t q_stride, int64_t out_stride, int64_t req_to_token_stride,
+                     float sm_scale, int window, const float* sinks, const float* slopes, float qtemp_coef,
+                     int qtemp_every, int dtype, spd_stream_t stream);
+/* Retention (linear attention with a fixed per-head decay, no softmax): per head
+ *   S_t = decay[h] S_(t-1) + k_t v_t^T,  o_t = S_t^T q_t
+ * with q, k rotated over their first rot_dims dimensions (rotate-half pairing, cos_sin [positions,
+ * rot_dims] fp32 = cos || sin) and k scaled by k_scale afterwards.  state [slots, heads, head_dim, v_dim]
+ * fp32 is read at slot req_pool_indices[r] unless the request starts at position 0 (zero state then),
+ * and written back.  Decode (seq_lens != NULL) or ragged extend as spd_attn_general; in decode rows
+ * whose out_cache_loc is 0 (padding of a captured batch) leave the state untouched.  o fp32 [tokens,
+ * heads * v_dim]. */
+int spd_retention(float* o, const void* q, const void* k, const void* v, float* state,
+                  const int64_t* req_pool_indices, const int64_t* seq_lens, const int64_t* out_cache_loc,
+                  const int32_t* prefix_lens, const int32_t* extend_lens, const int32_t* extend_start_loc,
+                  int64_t batch, int num_heads, int head_dim, int v_dim, int64_t q_stride, int64_t k_stride,
+                  int64_t v_stride, const float* decay, const float* cos_sin, int rot_dims,
+                  int64_t max_positions, float k_scale, int dtype, spd_stream_t stream);
 
 #ifdef __cplusplus
 }

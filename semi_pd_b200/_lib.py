@@ -19,6 +19,7 @@ HEADER_PATH = os.path.join(os.path.dirname(_HERE), "include", "spd.h")
 
 SPD_BF16 = 0
 SPD_F16 = 1
+SPD_F32 = 2
 SPD_EPI_NONE = 0
 SPD_EPI_SILU_MUL = 1
 
@@ -88,6 +89,25 @@ SIGNATURES = {
     "spd_attn_mla_workspace_bytes": (_i64, [_i, _i]),
     "spd_attn_mla": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i, _i, _i, _i64, _i64, _i64, _f, _i, _p,
                           _i64, _i, _p]),
+    "spd_residual_rmsnorm": (_i, [_p, _p, _p, _p, _p, _i64, _i64, _f, _f, _i, _p]),
+    "spd_embed_f32": (_i, [_p, _p, _p, _i64, _i64, _i64, _i, _p]),
+    "spd_act_and_mul": (_i, [_p, _p, _i64, _i64, _i, _i, _p]),
+    "spd_headnorm_gate": (_i, [_p, _p, _p, _i64, _i, _i, _i64, _f, _i, _p]),
+    "spd_linear_simt": (_i, [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _p, _i64, _i, _i, _p]),
+    "spd_moe_route_scores": (_i, [_p, _p, _p, _i64, _i64, _i, _i, _i, _i, _f, _p]),
+    "spd_moe_gather_scaled": (_i, [_p, _p, _p, _p, _p, _i64, _i, _i64, _i64, _i, _p]),
+    "spd_moe_combine_gated": (_i, [_p, _p, _p, _p, _p, _p, _i64, _i64, _i, _i64, _i, _p]),
+    "spd_kv_store": (_i, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i, _p]),
+    "spd_attn_general": (
+        _i,
+        [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i, _i, _i, _i, _i64, _i64, _i64, _f, _i, _p, _p,
+         _f, _i, _i, _p],
+    ),
+    "spd_retention": (
+        _i,
+        [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i, _i, _i, _i64, _i64, _i64, _p, _p, _i, _i64, _f,
+         _i, _p],
+    ),
     "spd_attn_prefill_simt": (
         _i,
         [_p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i, _i, _i, _i64, _i64, _i64, _f, _i, _p],

@@ -65,7 +65,9 @@ class RadixAttention:
 
     def __init__(self, num_heads: int, head_dim: int, scaling: float, num_kv_heads: int,
                  layer_id: int, logit_cap: float = 0.0, v_head_dim: int = -1,
-                 sliding_window_size: int = -1, is_cross_attention: bool = False, prefix: str = ""):
+                 sliding_window_size: int = -1, is_cross_attention: bool = False, prefix: str = "",
+                 sinks: Optional[torch.Tensor] = None, distance_slopes: Optional[torch.Tensor] = None,
+                 query_temperature: Optional[tuple] = None, general: bool = False):
         self.tp_q_head_num = num_heads
         self.tp_k_head_num = num_kv_heads
         self.tp_v_head_num = num_kv_heads
@@ -77,6 +79,16 @@ class RadixAttention:
         self.logit_cap = logit_cap
         self.sliding_window_size = sliding_window_size or -1
         self.is_cross_attention = is_cross_attention
+        # options only the general kernel (csrc/attn_general.cu) has: a learned per-head sink in the
+        # softmax denominator (fp32 [heads]), a per-head slope of a linear distance bias (fp32
+        # [heads]), a query temperature (coef, every): q · (1 + coef · ln(floor((pos + 1) / every) + 1)).
+        # `general` routes the layer there; it is implied by any of them, by a window, and by
+        # key size != value size.
+        self.sinks = sinks
+        self.distance_slopes = distance_slopes
+        self.query_temperature = query_temperature
+        self.general = bool(general or sinks is not None or distance_slopes is not None or query_temperature
+                            or self.sliding_window_size > 0 or self.v_head_dim != self.qk_head_dim)
         self.k_scale = None
         self.v_scale = None
 
@@ -99,6 +111,12 @@ class SpdAttnBackend(AttentionBackend):
         self.num_q_heads = model_runner.model_config.num_attention_heads // model_runner.tp_size
         self.head_dim = model_runner.model_config.head_dim
         self.is_mla = getattr(model_runner.model_config, "model_type", "llama") == "deepseek_v2"
+        self.mla_workspace = self.decode_workspace = None
+        if getattr(model_runner.model_config, "layer_specs", None) is not None:
+            # hybrid family: every layer runs the general kernel or a retention mixer, neither of
+            # which needs a workspace or a host-side plan
+            self.impl = "general"
+            return
         # "tc" = tcgen05 kernels (the product path, head_dim 128); "simt" exists for bring-up /
         # cross-checks and serves the head_dim-64 plumbing model (OPT-125m, BASELINE configs[0])
         self.impl = os.environ.get("SPD_ATTN_IMPL", "tc" if self.head_dim == 128 else "simt")
@@ -142,11 +160,43 @@ class SpdAttnBackend(AttentionBackend):
     def get_cuda_graph_seq_len_fill_value(self):
         return 1
 
+    def _forward_general(self, q, layer: RadixAttention, forward_batch: ForwardBatch):
+        """Window / sink / distance bias / query temperature / k_dim != v_dim / float32: the general
+        kernel, decode and ragged extend alike, reading the batch's device-side metadata."""
+        k_buf, v_buf = forward_batch.token_to_kv_pool.get_kv_buffer(layer.layer_id)
+        coef, every = layer.query_temperature or (0.0, 0)
+        common = dict(num_q_heads=layer.tp_q_head_num, num_kv_heads=layer.tp_k_head_num, head_dim=layer.qk_head_dim,
+                      v_dim=layer.v_head_dim, sm_scale=layer.scaling, window=layer.sliding_window_size,
+                      sinks=layer.sinks, slopes=layer.distance_slopes, qtemp_coef=coef, qtemp_every=every)
+        r2t = forward_batch.req_to_token_pool.req_to_token
+        if forward_batch.forward_mode.is_decode():
+            return ops.attn_general(q, k_buf, v_buf, r2t, forward_batch.req_pool_indices,
+                                    seq_lens=forward_batch.seq_lens, **common)
+        return ops.attn_general(q, k_buf, v_buf, r2t, forward_batch.req_pool_indices,
+                                prefix_lens=forward_batch.extend_prefix_lens, extend_lens=forward_batch.extend_seq_lens,
+                                extend_start_loc=forward_batch.extend_start_loc, **common)
+
+    def forward_retention(self, q, k, v, layer, forward_batch: ForwardBatch):
+        """Retention mixer (decayed linear attention) over the request's recurrent state slot;
+        `layer` carries num_heads, head_dim, v_head_dim, decay (fp32 [heads]), cos_sin_cache, rotary_dim,
+        k_scale and layer_id.  → o fp32 [T, heads · v_head_dim]; the state is updated in place."""
+        state = forward_batch.token_to_kv_pool.state_pool.get_state(layer.layer_id)
+        common = dict(num_heads=layer.num_heads, head_dim=layer.head_dim, v_dim=layer.v_head_dim, decay=layer.decay,
+                      cos_sin=layer.cos_sin_cache, rot_dims=layer.rotary_dim, k_scale=layer.k_scale)
+        if forward_batch.forward_mode.is_decode():
+            return ops.retention(q, k, v, state, forward_batch.req_pool_indices, seq_lens=forward_batch.seq_lens,
+                                 out_cache_loc=forward_batch.out_cache_loc, **common)
+        return ops.retention(q, k, v, state, forward_batch.req_pool_indices,
+                             prefix_lens=forward_batch.extend_prefix_lens, extend_lens=forward_batch.extend_seq_lens,
+                             extend_start_loc=forward_batch.extend_start_loc, **common)
+
     def forward_extend(self, q, k, v, layer: RadixAttention, forward_batch: ForwardBatch,
                        save_kv_cache: bool = True):
         pool = forward_batch.token_to_kv_pool
         if save_kv_cache:
             pool.set_kv_buffer(layer, forward_batch.out_cache_loc, k, v)
+        if layer.general:
+            return self._forward_general(q, layer, forward_batch)
         k_buf, v_buf = pool.get_kv_buffer(layer.layer_id)
         return ops.attn_prefill(
             q, k_buf, v_buf, forward_batch.req_to_token_pool.req_to_token,
@@ -159,6 +209,8 @@ class SpdAttnBackend(AttentionBackend):
         pool = forward_batch.token_to_kv_pool
         if save_kv_cache:
             pool.set_kv_buffer(layer, forward_batch.out_cache_loc, k, v)
+        if layer.general:
+            return self._forward_general(q, layer, forward_batch)
         k_buf, v_buf = pool.get_kv_buffer(layer.layer_id)
         return ops.attn_decode(
             q, k_buf, v_buf, forward_batch.req_to_token_pool.req_to_token,

@@ -8,6 +8,7 @@ environment variables are python/sglang/semi_pd/utils.py:10-11,25-28.
 from __future__ import annotations
 
 import dataclasses
+import json
 import os
 from enum import Enum
 from typing import List, Optional
@@ -60,6 +61,9 @@ class ModelConfig:
     moe_layer_freq: int = 1
     routed_scaling_factor: float = 1.0
     norm_topk_prob: bool = False
+    # hybrid family (model_type "rimidra"): one entry per layer — {"type": "attention" | "retention",
+    # "mixer": {...sizes and constants...}, "mlp": {...} | None, "weights_of": j (optional)}
+    layer_specs: Optional[List[dict]] = None
 
     @property
     def context_len(self) -> int:
@@ -100,7 +104,49 @@ _PRESETS = {
 }
 
 
+def _rimidra_config(path: str, cfg: dict, **overrides) -> ModelConfig:
+    """config.json of the Rimidra family: {"architecture", "vocab", "width", "norm": {"eps"},
+    "layers": [{"type", "mixer", "mlp", "weights_of"?}, ...]} — every size and constant of a layer is
+    carried per layer in `layer_specs`; nothing is assumed equal across layers."""
+    layers = cfg["layers"]
+    for i, spec in enumerate(layers):
+        if spec["type"] not in ("attention", "retention"):
+            raise ValueError(f"layer {i}: unknown mixer type {spec['type']!r}")
+        j = spec.get("weights_of")
+        if j is not None and (not 0 <= j < len(layers) or layers[j].get("weights_of") is not None
+                              or layers[j]["type"] != spec["type"]):
+            raise ValueError(f"layer {i}: weights_of {j} must name a layer of the same type with tensors of its own")
+    attn = [s["mixer"] for s in layers if s["type"] == "attention"]
+    kw = dict(model_type="rimidra", hidden_size=int(cfg["width"]), vocab_size=int(cfg["vocab"]),
+              num_hidden_layers=len(layers), rms_norm_eps=float(cfg["norm"]["eps"]), layer_specs=layers,
+              # summary fields other components print or size by; the per-layer values rule
+              num_attention_heads=max([m["heads"] for m in attn] or [1]),
+              num_key_value_heads=max([m["kv_heads"] for m in attn] or [1]),
+              head_dim=max([m["dim"] for m in attn] or [1]), intermediate_size=0,
+              max_position_embeddings=int(cfg.get("context", 8192)))
+    kw.update(overrides)
+    return ModelConfig(name=os.path.basename(os.path.normpath(path)) or "rimidra", **kw)
+
+
+# config.json "architecture" -> reader
+_ARCHITECTURE_READERS = {"Rimidra": _rimidra_config}
+
+
+def load_model_config(path: str, **overrides) -> ModelConfig:
+    """ModelConfig of a model folder (config.json [+ model.safetensors]); the architecture named
+    there selects the reader, as the `architectures` list of an HF config selects the model class
+    in the reference (python/sglang/srt/model_loader/utils.py)."""
+    with open(os.path.join(path, "config.json")) as f:
+        cfg = json.load(f)
+    arch = cfg.get("architecture") or (cfg.get("architectures") or [None])[0]
+    if arch not in _ARCHITECTURE_READERS:
+        raise ValueError(f"{path}: architecture {arch!r} is not supported; known: {sorted(_ARCHITECTURE_READERS)}")
+    return _ARCHITECTURE_READERS[arch](path, cfg, **overrides)
+
+
 def get_model_config(name: str, **overrides) -> ModelConfig:
+    if os.path.isdir(name) and os.path.exists(os.path.join(name, "config.json")):
+        return load_model_config(name, **overrides)
     key = name.lower().split("/")[-1]
     for cand in (key, key.replace("meta-", ""), key.replace("-instruct", "")):
         if cand in _PRESETS:
@@ -119,7 +165,9 @@ def default_cuda_graph_bs(max_bs: int = 160) -> List[int]:
 class ServerArgs:
     model_path: str = "llama-3-8b"
     dtype: str = "bfloat16"
-    load_format: str = "dummy"          # synthetic weights; there is no checkpoint loader here
+    # "dummy": synthetic weights; "safetensors": <model_path>/model.safetensors; "auto": the file
+    # when model_path is a folder that has one, else dummy; "external": load_weights() by the caller
+    load_format: str = "dummy"
     tp_size: int = 1
     mem_fraction_static: Optional[float] = None
     max_total_tokens: Optional[int] = None
@@ -141,8 +189,9 @@ class ServerArgs:
     device: str = "cuda"
 
     def torch_dtype(self) -> torch.dtype:
+        # float32: the hybrid family only (its operators exist in true 32-bit)
         return {"bfloat16": torch.bfloat16, "float16": torch.float16, "half": torch.float16,
-                "auto": torch.bfloat16}[self.dtype]
+                "auto": torch.bfloat16, "float32": torch.float32}[self.dtype]
 
     @staticmethod
     def add_cli_args(parser):

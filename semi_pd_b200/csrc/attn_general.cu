@@ -1,0 +1,208 @@
+// Softmax attention over the paged KV pool with the options the tcgen05 kernels do not have:
+// a sliding window, a learned per-head sink in the denominator, a linear distance bias, a
+// position-dependent query temperature, key size != value size, and 32-bit storage.  Decode and
+// ragged extend (chunked prefill, mixed batches) are the same kernel: one warp owns one (query
+// token, query head), walks its visible keys in tiles of 32 (one key per lane for the scores, one
+// slice of the value row per lane for the output) and keeps the online-softmax state in fp32.
+// The four warps of a CTA are four consecutive tokens of one head, so their K/V rows meet in L1.
+// Beside attn_simt.cu (plain causal SIMT attention) in role; the reference has no such kernel.
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace spd {
+
+constexpr int kGenMaxVPerLane = 8;   // v_dim <= 256
+constexpr int kGenMaxHeadDim = 256;
+
+template <typename T>
+__device__ __forceinline__ float dot_row(const float* __restrict__ qs, const T* __restrict__ krow, int dk);
+
+template <>
+__device__ __forceinline__ float dot_row<float>(const float* __restrict__ qs, const float* __restrict__ krow, int dk) {
+  float s = 0.f;
+  if ((dk & 3) == 0 && (reinterpret_cast<uintptr_t>(krow) & 15u) == 0) {
+    for (int d = 0; d < dk; d += 4) {
+      const float4 kv = *reinterpret_cast<const float4*>(krow + d);
+      s = fmaf(qs[d], kv.x, s);
+      s = fmaf(qs[d + 1], kv.y, s);
+      s = fmaf(qs[d + 2], kv.z, s);
+      s = fmaf(qs[d + 3], kv.w, s);
+    }
+  } else {
+    for (int d = 0; d < dk; ++d) s = fmaf(qs[d], krow[d], s);
+  }
+  return s;
+}
+
+template <typename T>
+__device__ __forceinline__ float dot_row(const float* __restrict__ qs, const T* __restrict__ krow, int dk) {
+  float s = 0.f;
+  if ((dk & 7) == 0 && (reinterpret_cast<uintptr_t>(krow) & 15u) == 0) {
+    for (int d = 0; d < dk; d += 8) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(krow + d);
+      const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) s = fmaf(qs[d + i], to_f32<T>(e[i]), s);
+    }
+  } else {
+    for (int d = 0; d < dk; ++d) s = fmaf(qs[d], to_f32<T>(krow[d]), s);
+  }
+  return s;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+attn_general_kernel(T* __restrict__ out, const T* __restrict__ q, const T* __restrict__ k_pool,
+                    const T* __restrict__ v_pool, const int32_t* __restrict__ req_to_token,
+                    const int64_t* __restrict__ req_pool_indices, const int64_t* __restrict__ seq_lens,
+                    const int32_t* __restrict__ prefix_lens, const int32_t* __restrict__ extend_lens,
+                    const int32_t* __restrict__ extend_start_loc, int batch, int64_t total_tokens, int H, int G,
+                    int dk, int dv, int64_t q_stride, int64_t out_stride, int64_t r2t_stride, float sm_scale,
+                    int window, const float* __restrict__ sinks, const float* __restrict__ slopes, float qtemp_coef,
+                    int qtemp_every) {
+  griddep_wait();
+  griddep_launch_dependents();
+  extern __shared__ float q_smem[];  // [4][dk]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  // item = h * tokens_padded + t with tokens_padded a multiple of 4: the warps of a CTA share a head
+  const int64_t tokens4 = (total_tokens + 3) / 4 * 4;
+  const int64_t item = blockIdx.x * 4ll + warp;
+  const int h = (int)(item / tokens4);
+  const int64_t t = item - (int64_t)h * tokens4;
+  if (h >= H || t >= total_tokens) return;  // warp-uniform; no block-level barrier below
+
+  int r;
+  int64_t pos;
+  if (seq_lens != nullptr) {
+    r = (int)t;
+    pos = seq_lens[r] - 1;
+  } else {
+    int lo = 0, hi = batch - 1;  // last request whose first row is <= t and that is not empty
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if ((int64_t)extend_start_loc[mid] <= t) lo = mid; else hi = mid - 1;
+    }
+    r = lo;
+    while (r > 0 && extend_lens[r] == 0) --r;  // (empty entries share their successor's start)
+    pos = (int64_t)prefix_lens[r] + (t - extend_start_loc[r]);
+  }
+  if (pos < 0) return;
+  const int32_t* page = req_to_token + req_pool_indices[r] * r2t_stride;
+  const int g = h / (H / G);
+
+  float* qs = q_smem + warp * dk;
+  float temp = 1.f;
+  if (qtemp_every > 0) temp = 1.f + qtemp_coef * logf((float)((pos + 1) / qtemp_every + 1));
+  const float qmul = sm_scale * temp;
+  for (int d = lane; d < dk; d += 32) qs[d] = to_f32<T>(q[t * q_stride + (int64_t)h * dk + d]) * qmul;
+  __syncwarp();
+
+  const float slope = slopes != nullptr ? slopes[h] : 0.f;
+  float m = -INFINITY, l = 0.f;
+  if (sinks != nullptr) { m = sinks[h]; l = 1.f; }
+  float acc[kGenMaxVPerLane];
+#pragma unroll
+  for (int i = 0; i < kGenMaxVPerLane; ++i) acc[i] = 0.f;
+
+  const int64_t j_lo = window > 0 ? (pos - window + 1 > 0 ? pos - window + 1 : 0) : 0;
+  for (int64_t j0 = j_lo; j0 <= pos; j0 += 32) {
+    const int64_t j = j0 + lane;
+    const bool valid = j <= pos;
+    int slot = 0;
+    float s = -INFINITY;
+    if (valid) {
+      slot = page[j];
+      s = dot_row<T>(qs, k_pool + ((int64_t)slot * G + g) * dk, dk) - slope * (float)(pos - j);
+    }
+    const float m_new = fmaxf(m, warp_max(s));
+    const float corr = expf(m - m_new);  // m = -inf (first tile, no sink): 0
+    const float p = valid ? expf(s - m_new) : 0.f;
+    l = l * corr + warp_sum(p);
+    m = m_new;
+#pragma unroll
+    for (int i = 0; i < kGenMaxVPerLane; ++i) acc[i] *= corr;
+    const int n = (int)(pos - j0 + 1 < 32 ? pos - j0 + 1 : 32);
+    for (int jj = 0; jj < n; ++jj) {
+      const float pj = __shfl_sync(0xffffffffu, p, jj);
+      const int sj = __shfl_sync(0xffffffffu, slot, jj);
+      const T* vrow = v_pool + ((int64_t)sj * G + g) * dv;
+#pragma unroll
+      for (int i = 0; i < kGenMaxVPerLane; ++i) {
+        const int c = lane + 32 * i;
+        if (c < dv) acc[i] = fmaf(pj, to_f32<T>(vrow[c]), acc[i]);
+      }
+    }
+  }
+  const float inv = 1.0f / l;
+#pragma unroll
+  for (int i = 0; i < kGenMaxVPerLane; ++i) {
+    const int c = lane + 32 * i;
+    if (c < dv) out[t * out_stride + (int64_t)h * dv + c] = from_f32<T>(acc[i] * inv);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+kv_store_kernel(const T* __restrict__ k, const T* __restrict__ v, T* __restrict__ k_pool, T* __restrict__ v_pool,
+                const int64_t* __restrict__ loc, int64_t k_row, int64_t v_row, int64_t k_stride, int64_t v_stride) {
+  griddep_wait();
+  griddep_launch_dependents();
+  const int64_t t = blockIdx.x;
+  const int64_t slot = loc[t];
+  for (int64_t i = threadIdx.x; i < k_row; i += 256) k_pool[slot * k_row + i] = k[t * k_stride + i];
+  if (v != nullptr)
+    for (int64_t i = threadIdx.x; i < v_row; i += 256) v_pool[slot * v_row + i] = v[t * v_stride + i];
+}
+
+}  // namespace spd
+
+using namespace spd;
+
+extern "C" {
+
+int spd_kv_store(const void* k, const void* v, void* k_pool, void* v_pool, const int64_t* loc,
+                 int64_t tokens, int64_t k_row_elems, int64_t v_row_elems, int64_t k_stride,
+                 int64_t v_stride, int dtype, spd_stream_t stream) {
+  SPD_REQUIRE(k && k_pool && loc && (v == nullptr || v_pool), SPD_E_BADARG, "spd_kv_store: null pointer");
+  SPD_REQUIRE(tokens >= 0 && k_row_elems > 0 && v_row_elems >= 0, SPD_E_BADARG, "spd_kv_store: bad sizes");
+  if (tokens == 0) return 0;
+  SPD_DISPATCH_ANY(dtype, {
+    SPD_CUDA(launch(kv_store_kernel<T>, dim3((unsigned)tokens), dim3(256), 0, as_stream(stream), pdl_enabled(),
+                    (const T*)k, (const T*)v, (T*)k_pool, (T*)v_pool, loc, k_row_elems, v_row_elems, k_stride,
+                    v_stride));
+  });
+  return 0;
+}
+
+int spd_attn_general(void* out, const void* q, const void* k_pool, const void* v_pool,
+                     const int32_t* req_to_token, const int64_t* req_pool_indices, const int64_t* seq_lens,
+                     const int32_t* prefix_lens, const int32_t* extend_lens, const int32_t* extend_start_loc,
+                     int64_t batch, int64_t total_tokens, int num_q_heads, int num_kv_heads, int head_dim,
+                     int v_dim, int64_t q_stride, int64_t out_stride, int64_t req_to_token_stride,
+                     float sm_scale, int window, const float* sinks, const float* slopes, float qtemp_coef,
+                     int qtemp_every, int dtype, spd_stream_t stream) {
+  SPD_REQUIRE(out && q && k_pool && v_pool && req_to_token && req_pool_indices, SPD_E_BADARG,
+              "spd_attn_general: null pointer");
+  SPD_REQUIRE(seq_lens != nullptr || (prefix_lens && extend_lens && extend_start_loc), SPD_E_BADARG,
+              "spd_attn_general: extend needs prefix_lens, extend_lens and extend_start_loc");
+  SPD_REQUIRE(num_q_heads > 0 && num_kv_heads > 0 && num_q_heads % num_kv_heads == 0, SPD_E_SHAPE,
+              "spd_attn_general: heads %d not a multiple of kv heads %d", num_q_heads, num_kv_heads);
+  SPD_REQUIRE(head_dim > 0 && head_dim <= kGenMaxHeadDim && v_dim > 0 && v_dim <= 32 * kGenMaxVPerLane, SPD_E_SHAPE,
+              "spd_attn_general: head_dim %d / v_dim %d above %d", head_dim, v_dim, kGenMaxHeadDim);
+  SPD_REQUIRE(seq_lens == nullptr || batch == total_tokens, SPD_E_BADARG, "spd_attn_general: decode has one row per request");
+  if (total_tokens == 0 || batch == 0) return 0;
+  const int64_t tokens4 = (total_tokens + 3) / 4 * 4;
+  const int64_t ctas = tokens4 / 4 * num_q_heads;
+  SPD_REQUIRE(ctas < (1ll << 31), SPD_E_SHAPE, "spd_attn_general: batch too large");
+  const size_t smem = 4 * (size_t)head_dim * sizeof(float);
+  SPD_DISPATCH_ANY(dtype, {
+    SPD_CUDA(launch(attn_general_kernel<T>, dim3((unsigned)ctas), dim3(128), smem, as_stream(stream), pdl_enabled(),
+                    (T*)out, (const T*)q, (const T*)k_pool, (const T*)v_pool, req_to_token, req_pool_indices, seq_lens,
+                    prefix_lens, extend_lens, extend_start_loc, (int)batch, total_tokens, num_q_heads, num_kv_heads,
+                    head_dim, v_dim, q_stride, out_stride, req_to_token_stride, sm_scale, window, sinks, slopes,
+                    qtemp_coef, qtemp_every));
+  });
+  return 0;
+}
+
+}  // extern "C"

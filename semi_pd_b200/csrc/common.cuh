@@ -57,6 +57,23 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
     }                                                                   \
   } while (0)
 
+// dtype dispatch for the kernels that also run in true 32-bit: bf16, fp16 or float
+#define SPD_DISPATCH_ANY(dtype, ...)                                    \
+  do {                                                                  \
+    if ((dtype) == SPD_BF16) {                                          \
+      using T = __nv_bfloat16;                                          \
+      __VA_ARGS__                                                       \
+    } else if ((dtype) == SPD_F16) {                                    \
+      using T = __half;                                                 \
+      __VA_ARGS__                                                       \
+    } else if ((dtype) == SPD_F32) {                                    \
+      using T = float;                                                  \
+      __VA_ARGS__                                                       \
+    } else {                                                            \
+      return ::spd::set_error(SPD_E_BADARG, "bad dtype %d", (dtype));   \
+    }                                                                   \
+  } while (0)
+
 inline cudaStream_t as_stream(spd_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
 
 int device_sm_count_cached();

@@ -79,6 +79,10 @@ class ModelWorkerBatch:
     # TP > 1: all-gather the vocab-sharded logits (logits_processor.py:426-427).  The semi-PD
     # schedulers sample greedy ids from the (max, argmax) rows and never read the logits.
     gather_logits: bool = True
+    # extend only: rows of this batch's token list whose logits are wanted instead of every request's
+    # last token (int64, device) — the role of the reference's input-logprob positions
+    # (extend_logprob_start_lens, logits_processor.py:262-330), as explicit rows
+    extend_logit_rows: Optional[torch.Tensor] = None
 
 
 @dataclasses.dataclass
@@ -103,6 +107,7 @@ class ForwardBatch:
 
     return_logprob: bool = False
     gather_logits: bool = True
+    extend_logit_rows: Optional[torch.Tensor] = None
     positions: torch.Tensor = None
     decode_seq_lens_cpu: Optional[torch.Tensor] = None
 
@@ -135,6 +140,7 @@ class ForwardBatch:
             seq_lens_sum=batch.seq_lens_sum,
             return_logprob=batch.return_logprob,
             gather_logits=batch.gather_logits,
+            extend_logit_rows=batch.extend_logit_rows,
             sampling_info=batch.sampling_info,
             req_to_token_pool=model_runner.req_to_token_pool,
             token_to_kv_pool=model_runner.token_to_kv_pool,

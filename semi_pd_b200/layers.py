@@ -249,14 +249,21 @@ class LogitsProcessor:
         self.config = config
         self.do_tensor_parallel_all_gather = get_tensor_model_parallel_world_size() > 1
 
+    @staticmethod
+    def logit_rows(forward_batch: ForwardBatch) -> Optional[torch.Tensor]:
+        """Rows of the batch whose logits are computed: None = all (decode); the rows a caller asked
+        for (`extend_logit_rows`); else every request's last token."""
+        if forward_batch.forward_mode.is_decode_or_idle():
+            return None
+        if forward_batch.extend_logit_rows is not None:
+            return forward_batch.extend_logit_rows
+        # last_index = cumsum(extend_seq_lens) - 1  (logits_processor.py:244)
+        return forward_batch.extend_start_loc.long() + forward_batch.extend_seq_lens.long() - 1
+
     def forward(self, input_ids, hidden_states, lm_head, forward_batch: ForwardBatch
                 ) -> LogitsProcessorOutput:
-        if forward_batch.forward_mode.is_decode_or_idle():
-            pruned_states = hidden_states
-        else:
-            # last_index = cumsum(extend_seq_lens) - 1  (logits_processor.py:244)
-            last_index = forward_batch.extend_start_loc.long() + forward_batch.extend_seq_lens.long() - 1
-            pruned_states = ops.gather_rows(hidden_states, last_index)
+        rows = self.logit_rows(forward_batch)
+        pruned_states = hidden_states if rows is None else ops.gather_rows(hidden_states, rows)
         logits = ops.linear(pruned_states, lm_head.weight, out_f32=True)
         next_ids = None
         if self.do_tensor_parallel_all_gather:

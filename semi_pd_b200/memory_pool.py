@@ -377,3 +377,81 @@ class MLATokenToKVPool(KVCache):
         if cache_k.dtype != self.dtype:
             raise RuntimeError("KV cache dtype conversion is not on the semi-PD path")
         ops.kv_write_single(cache_k, self.kv_buffer[layer.layer_id], loc)
+
+
+class RecurrentStatePool:
+    """Per-request recurrent state of the layers that carry one (retention mixers): for such a
+    layer l, `state[l]` is fp32 [slots, heads, head_dim, v_dim], indexed by the request's
+    `req_pool_idx` — the slot `ReqToTokenPool` hands out, so a state slot is taken, reused and freed
+    with its request and needs no allocator of its own.  A kernel that starts a request at position
+    0 ignores what the slot held before (no clearing on reuse).  `layer_shapes[l]` is (heads,
+    head_dim, v_dim) or None for layers without state."""
+
+    def __init__(self, num_slots: int, layer_shapes: Sequence[Optional[Tuple[int, int, int]]], device: str):
+        self.num_slots = num_slots
+        self.layer_shapes = list(layer_shapes)
+        self.device = device
+        self.state: List[Optional[torch.Tensor]] = [
+            torch.zeros((num_slots,) + tuple(s), dtype=torch.float32, device=device) if s is not None else None
+            for s in self.layer_shapes]
+
+    @staticmethod
+    def bytes_per_slot(layer_shapes: Sequence[Optional[Tuple[int, int, int]]]) -> int:
+        return sum(4 * s[0] * s[1] * s[2] for s in layer_shapes if s is not None)
+
+    def get_state(self, layer_id: int) -> torch.Tensor:
+        return self.state[layer_id]
+
+
+class HybridTokenToKVPool(KVCache):
+    """KV pool of a model whose layers differ: layer l with `layer_shapes[l]` = (kv_heads, k_dim,
+    v_dim) owns k_buffer[l] [size + 1, kv_heads, k_dim] and v_buffer[l] [size + 1, kv_heads, v_dim]
+    (key and value sizes may differ); layers with None (recurrent mixers) own nothing here.  All
+    layers share the slot ids of one TokenToKVPoolAllocator, as in MHATokenToKVPool.  `dtype` may be
+    float32.  The recurrent layers' state pool travels with this object (`state_pool`), so both
+    workers of a GPU see it through the one pool they already share."""
+
+    def __init__(self, size: int, page_size: int, dtype: torch.dtype,
+                 layer_shapes: Sequence[Optional[Tuple[int, int, int]]], device: str,
+                 state_pool: Optional[RecurrentStatePool] = None):
+        if page_size != 1:
+            raise NotImplementedError("semi-PD path is token-granular: page_size must be 1")
+        self.size = size
+        self.page_size = page_size
+        self.dtype = dtype
+        self.store_dtype = dtype
+        self.device = device
+        self.layer_shapes = list(layer_shapes)
+        self.layer_num = len(self.layer_shapes)
+        self.state_pool = state_pool
+        rows = size + page_size
+        self.k_buffer: List[Optional[torch.Tensor]] = []
+        self.v_buffer: List[Optional[torch.Tensor]] = []
+        for s in self.layer_shapes:
+            self.k_buffer.append(torch.zeros((rows, s[0], s[1]), dtype=dtype, device=device) if s else None)
+            self.v_buffer.append(torch.zeros((rows, s[0], s[2]), dtype=dtype, device=device) if s else None)
+
+    @staticmethod
+    def bytes_per_token(layer_shapes, dtype: torch.dtype) -> int:
+        esz = torch.empty((), dtype=dtype).element_size()
+        return sum(s[0] * (s[1] + s[2]) * esz for s in layer_shapes if s is not None)
+
+    def get_kv_size_bytes(self):
+        k = sum(b.numel() * b.element_size() for b in self.k_buffer if b is not None)
+        v = sum(b.numel() * b.element_size() for b in self.v_buffer if b is not None)
+        return k, v
+
+    def get_key_buffer(self, layer_id: int):
+        return self.k_buffer[layer_id]
+
+    def get_value_buffer(self, layer_id: int):
+        return self.v_buffer[layer_id]
+
+    def get_kv_buffer(self, layer_id: int):
+        return self.k_buffer[layer_id], self.v_buffer[layer_id]
+
+    def set_kv_buffer(self, layer, loc: torch.Tensor, cache_k: torch.Tensor, cache_v: torch.Tensor,
+                      k_scale=None, v_scale=None):
+        if cache_k.dtype != self.dtype:
+            raise RuntimeError("KV cache dtype conversion is not on the semi-PD path")
+        ops.kv_store(cache_k, cache_v, self.k_buffer[layer.layer_id], self.v_buffer[layer.layer_id], loc)

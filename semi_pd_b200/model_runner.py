@@ -14,6 +14,7 @@ from __future__ import annotations
 import bisect
 import dataclasses
 import logging
+import os
 from typing import Optional
 
 import torch
@@ -26,7 +27,9 @@ from .distributed import TpComm, init_distributed_environment, set_current_comm
 from .forward_batch_info import ForwardBatch, ForwardMode, LogitsProcessorOutput
 from .layers import Sampler
 from .llama import LlamaForCausalLM
-from .memory_pool import MHATokenToKVPool, MLATokenToKVPool, ReqToTokenPool, TokenToKVPoolAllocator
+from .memory_pool import (HybridTokenToKVPool, MHATokenToKVPool, MLATokenToKVPool, RecurrentStatePool,
+                          ReqToTokenPool, TokenToKVPoolAllocator)
+from .registry import get_model_class
 
 logger = logging.getLogger(__name__)
 
@@ -92,26 +95,33 @@ class ModelRunner:
     # model + memory
     # ------------------------------------------------------------------------------------------
     def load_model(self):
-        if getattr(self.model_config, "model_type", "llama") == "opt":
-            from .opt import OPTForCausalLM
-            self.model = OPTForCausalLM(self.model_config, dtype=self.dtype, device=self.device)
-        elif self.model_config.model_type == "deepseek_v2":
-            from .deepseek_v2 import DeepseekV2ForCausalLM
-            self.model = DeepseekV2ForCausalLM(self.model_config, dtype=self.dtype, device=self.device)
-        else:
-            self.model = LlamaForCausalLM(self.model_config, dtype=self.dtype, device=self.device)
-        if self.server_args.load_format == "dummy":
+        model_type = getattr(self.model_config, "model_type", "llama")
+        if self.dtype == torch.float32 and getattr(self.model_config, "layer_specs", None) is None:
+            raise ValueError(f"--dtype float32: model_type {model_type!r} runs in 16-bit only")
+        self.model = get_model_class(model_type)(self.model_config, dtype=self.dtype, device=self.device)
+        fmt = self.server_args.load_format
+        path = self.server_args.model_path
+        if fmt == "auto":
+            from .weight_loader import model_weights_path
+            fmt = "safetensors" if os.path.isdir(path) and os.path.exists(model_weights_path(path)) else "dummy"
+        if fmt == "dummy":
             self.model.init_dummy_weights(self.server_args.random_seed)
-        elif self.server_args.load_format != "external":
-            raise NotImplementedError("only --load-format dummy (synthetic weights) or weights "
-                                      "passed through load_weights() are supported")
+        elif fmt == "safetensors":
+            from .weight_loader import model_weights_path, safetensors_weights_iterator
+            self.model.load_weights(safetensors_weights_iterator(model_weights_path(path)))
+        elif fmt != "external":
+            raise NotImplementedError("--load-format is one of dummy (synthetic weights), safetensors, auto, "
+                                      "external (weights passed through load_weights())")
 
     def profile_max_num_token(self, total_gpu_memory_bytes: int) -> int:
         """model_runner.py:924-949: tokens that fit in mem_fraction_static of the device after
         the weights."""
         cfg = self.model_config
         esz = torch.tensor([], dtype=self.kv_cache_dtype).element_size()
-        if getattr(cfg, "model_type", "llama") == "deepseek_v2":
+        if getattr(cfg, "layer_specs", None) is not None:
+            kv_shapes, _ = self.model.cache_shapes()
+            cell = max(HybridTokenToKVPool.bytes_per_token(kv_shapes, self.kv_cache_dtype), 64)
+        elif getattr(cfg, "model_type", "llama") == "deepseek_v2":
             cell = (cfg.kv_lora_rank + cfg.qk_rope_head_dim) * cfg.num_hidden_layers * esz  # model_runner.py:930-936
         else:
             cell = cfg.get_num_kv_heads(self.tp_size) * cfg.head_dim * cfg.num_hidden_layers * 2 * esz
@@ -127,12 +137,25 @@ class ModelRunner:
         self.max_total_num_tokens = min(profiled, max_total_tokens) if max_total_tokens else profiled
         if self.max_total_num_tokens <= 0:
             raise RuntimeError("Not enough memory. Please try to increase --mem-fraction-static.")
+        hybrid = getattr(cfg, "layer_specs", None) is not None
         if max_num_reqs is None:
             max_num_reqs = min(max(int(self.max_total_num_tokens / cfg.context_len * 512), 2048), 4096)
+            if hybrid:
+                # every request slot owns a recurrent state: keep the state pool within a tenth of the device
+                per = RecurrentStatePool.bytes_per_slot(self.model.cache_shapes()[1])
+                if per:
+                    total = torch.cuda.mem_get_info(self.device)[1]
+                    max_num_reqs = max(1, min(max_num_reqs, int(0.1 * total // per) - 1))
         ctx = self.server_args.context_length or cfg.context_len
         self.req_to_token_pool = ReqToTokenPool(size=max_num_reqs + 1, max_context_len=ctx + 4,
                                                 device=self.device)
-        if getattr(cfg, "model_type", "llama") == "deepseek_v2":
+        if hybrid:
+            kv_shapes, state_shapes = self.model.cache_shapes()
+            self.token_to_kv_pool = HybridTokenToKVPool(
+                self.max_total_num_tokens, page_size=1, dtype=self.kv_cache_dtype, layer_shapes=kv_shapes,
+                device=self.device,
+                state_pool=RecurrentStatePool(max_num_reqs + 1, state_shapes, device=self.device))
+        elif getattr(cfg, "model_type", "llama") == "deepseek_v2":
             self.token_to_kv_pool = MLATokenToKVPool(
                 self.max_total_num_tokens, page_size=1, dtype=self.kv_cache_dtype, kv_lora_rank=cfg.kv_lora_rank,
                 qk_rope_head_dim=cfg.qk_rope_head_dim, layer_num=cfg.num_hidden_layers, device=self.device)

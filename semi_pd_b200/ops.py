@@ -8,6 +8,7 @@ torch is plumbing here (device memory + streams); every computation runs in libs
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -16,6 +17,8 @@ from . import _lib
 from ._lib import SPD_EPI_NONE, SPD_EPI_SILU_MUL, check, lib
 
 _DTYPE = {torch.bfloat16: _lib.SPD_BF16, torch.float16: _lib.SPD_F16}
+# the 32-bit capable operators (hybrid model family) additionally take float32
+_DTYPE_ANY = {**_DTYPE, torch.float32: _lib.SPD_F32}
 
 
 def _dt(t: torch.Tensor) -> int:
@@ -23,6 +26,13 @@ def _dt(t: torch.Tensor) -> int:
         return _DTYPE[t.dtype]
     except KeyError:
         raise RuntimeError(f"libspd supports bfloat16/float16 tensors, got {t.dtype}") from None
+
+
+def _dta(t: torch.Tensor) -> int:
+    try:
+        return _DTYPE_ANY[t.dtype]
+    except KeyError:
+        raise RuntimeError(f"libspd supports bfloat16/float16/float32 tensors here, got {t.dtype}") from None
 
 
 def _stream() -> int:
@@ -512,6 +522,220 @@ def attn_prefill(q, k_pool, v_pool, req_to_token, req_pool_indices, prefix_lens,
     else:
         check(lib.spd_attn_prefill_simt(*args, _stream()), "spd_attn_prefill_simt")
     return out
+
+
+# ------------------------------------------------------------------------------------------------
+# 32-bit capable operators (hybrid model family: fp32 residual stream, windowed attention with
+# sinks, retention, sigmoid-routed experts that weight their input)
+# ------------------------------------------------------------------------------------------------
+def _ptr(t: Optional[torch.Tensor]):
+    return t.data_ptr() if t is not None else None
+
+
+def embed_f32(table: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
+    """fp32 [n, dim] rows of a 16/32-bit embedding table (the start of an fp32 residual stream)."""
+    _cuda(table, idx)
+    if idx.dtype != torch.int64:
+        idx = idx.long()
+    out = torch.empty((idx.numel(), table.shape[1]), device=table.device, dtype=torch.float32)
+    check(lib.spd_embed_f32(out.data_ptr(), table.data_ptr(), idx.data_ptr(), idx.numel(), table.shape[1],
+                            table.shape[0], _dta(table), _stream()), "spd_embed_f32")
+    return out
+
+
+def residual_rmsnorm(x: torch.Tensor, weight: Optional[torch.Tensor], eps: float, a: Optional[torch.Tensor] = None,
+                     b: Optional[torch.Tensor] = None, weight_offset: float = 0.0,
+                     out_dtype: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
+    """x (fp32, in place) += a (+ b); → x / sqrt(mean(x²) + eps) · (weight_offset + weight) in the
+    weight's dtype (None when weight is None: residual add only)."""
+    _cuda(x, weight, a, b)
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise RuntimeError("residual_rmsnorm: the residual stream is contiguous fp32")
+    for t in (a, b):
+        if t is not None and (not t.is_contiguous() or t.shape != x.shape):
+            raise RuntimeError("residual_rmsnorm: a / b must match x and be contiguous")
+    ref = weight if weight is not None else a
+    if a is not None and weight is not None and a.dtype != weight.dtype:
+        raise RuntimeError("residual_rmsnorm: a / b and weight must share a dtype")
+    d = x.shape[-1]
+    out = torch.empty(x.shape, device=x.device, dtype=ref.dtype) if weight is not None else None
+    check(lib.spd_residual_rmsnorm(_ptr(out), x.data_ptr(), _ptr(a), _ptr(b), _ptr(weight), x.numel() // d, d,
+                                   float(eps), float(weight_offset), _dta(ref), _stream()), "spd_residual_rmsnorm")
+    return out
+
+
+def act_and_mul(x: torch.Tensor, act: str = "silu") -> torch.Tensor:
+    """act(x[:, :I]) · x[:, I:], act in {"silu", "gelu_tanh"}; any of the three dtypes."""
+    _cuda(x)
+    if x.dim() != 2 or not x.is_contiguous():
+        raise RuntimeError("act_and_mul: x must be contiguous [rows, 2 I]")
+    inter = x.shape[1] // 2
+    out = torch.empty((x.shape[0], inter), device=x.device, dtype=x.dtype)
+    check(lib.spd_act_and_mul(out.data_ptr(), x.data_ptr(), x.shape[0], inter, {"silu": 0, "gelu_tanh": 1}[act],
+                              _dta(x), _stream()), "spd_act_and_mul")
+    return out
+
+
+def headnorm_gate(o: torch.Tensor, gate: torch.Tensor, heads: int, vdim: int, eps: float) -> torch.Tensor:
+    """o fp32 [T, heads·vdim] → per-head o / rms(o) · silu(gate), in gate's dtype."""
+    _cuda(o, gate)
+    if o.dtype != torch.float32 or not o.is_contiguous() or gate.stride(1) != 1:
+        raise RuntimeError("headnorm_gate: o is contiguous fp32, gate has contiguous rows")
+    T = o.shape[0]
+    out = torch.empty((T, heads * vdim), device=o.device, dtype=gate.dtype)
+    check(lib.spd_headnorm_gate(out.data_ptr(), o.data_ptr(), gate.data_ptr(), T, heads, vdim, gate.stride(0),
+                                float(eps), _dta(gate), _stream()), "spd_headnorm_gate")
+    return out
+
+
+def linear_simt(x: torch.Tensor, weight: torch.Tensor, out_f32: bool = False,
+                tile_group: Optional[torch.Tensor] = None, group_rows: int = 0, n: Optional[int] = None) -> torch.Tensor:
+    """F.linear on the CUDA cores (any shape / dtype, fp32 accumulation in ascending k).  With
+    tile_group, rows of x come in expert-aligned 128-row tiles and rows [g·group_rows, +n) of weight
+    multiply group g's tiles."""
+    _cuda(x, weight, tile_group)
+    if x.dim() != 2 or weight.dim() != 2 or x.stride(1) != 1 or weight.stride(1) != 1 or x.dtype != weight.dtype:
+        raise RuntimeError("linear_simt: x and weight must be 2-D, contiguous rows, same dtype")
+    M, K = x.shape
+    N = weight.shape[0] if n is None else n
+    out = torch.empty((M, N), device=x.device, dtype=torch.float32 if out_f32 else x.dtype)
+    check(lib.spd_linear_simt(out.data_ptr(), x.data_ptr(), weight.data_ptr(), M, N, K, x.stride(0), weight.stride(0),
+                              out.stride(0), _ptr(tile_group), int(group_rows), _dta(x), 1 if out_f32 else 0, _stream()),
+          "spd_linear_simt")
+    return out
+
+
+def _tc_gemm_ok(x: torch.Tensor, weight: torch.Tensor, n: int) -> bool:
+    """Shapes / dtypes the tcgen05 GEMMs take (16-bit, 16-byte rows and pointers)."""
+    return (x.dtype in _DTYPE and x.shape[1] % 8 == 0 and n % 8 == 0 and x.stride(0) % 8 == 0
+            and weight.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
+
+
+def linear_any(x: torch.Tensor, weight: torch.Tensor, out_f32: bool = False) -> torch.Tensor:
+    """F.linear for the hybrid family: the tcgen05 GEMMs where they apply (16-bit, aligned shapes),
+    the CUDA-core GEMM otherwise (float32 models, odd sizes)."""
+    if _tc_gemm_ok(x, weight, weight.shape[0]) and os.environ.get("SPD_HYBRID_GEMM", "tc") == "tc":
+        return linear(x, weight, out_f32=out_f32)
+    return linear_simt(x, weight, out_f32=out_f32)
+
+
+def linear_grouped_any(x_sorted: torch.Tensor, weight: torch.Tensor, tile_group: torch.Tensor, num_groups: int,
+                       n: int) -> torch.Tensor:
+    """Expert-grouped F.linear over 128-row tiles; weight = the experts' [n, K] matrices stacked."""
+    if (_tc_gemm_ok(x_sorted, weight, n) and x_sorted.shape[1] % 64 == 0
+            and os.environ.get("SPD_HYBRID_GEMM", "tc") == "tc"):
+        return linear_grouped_rows(x_sorted, weight, tile_group, num_groups, n)
+    return linear_simt(x_sorted, weight, tile_group=tile_group, group_rows=n, n=n)
+
+
+def moe_route_scores(logits: torch.Tensor, num_experts: int, top_k: int, score_func: str = "sigmoid",
+                     renormalize: bool = False, scale: float = 1.0):
+    """fp32 logits [T, >= E] (row stride free) → (topk_ids int32 [T, k], topk_weights fp32 [T, k])."""
+    _cuda(logits)
+    if logits.dtype != torch.float32 or logits.stride(1) != 1:
+        raise RuntimeError("moe_route_scores: logits are fp32 with contiguous rows")
+    T = logits.shape[0]
+    ids = torch.empty((T, top_k), device=logits.device, dtype=torch.int32)
+    w = torch.empty((T, top_k), device=logits.device, dtype=torch.float32)
+    check(lib.spd_moe_route_scores(ids.data_ptr(), w.data_ptr(), logits.data_ptr(), logits.stride(0), T, num_experts,
+                                   top_k, {"softmax": 0, "sigmoid": 1}[score_func], 1 if renormalize else 0,
+                                   float(scale), _stream()), "spd_moe_route_scores")
+    return ids, w
+
+
+def moe_gather_scaled(x: torch.Tensor, row_token: torch.Tensor, inv_pos: torch.Tensor,
+                      topk_w: Optional[torch.Tensor]) -> torch.Tensor:
+    """Expert-sorted rows of x, each multiplied by its routing weight (experts that weight their input)."""
+    _cuda(x, row_token, inv_pos, topk_w)
+    k = topk_w.shape[1] if topk_w is not None else inv_pos.numel() // max(x.shape[0], 1)
+    out = torch.empty((row_token.numel(), x.shape[1]), device=x.device, dtype=x.dtype)
+    check(lib.spd_moe_gather_scaled(out.data_ptr(), x.data_ptr(), row_token.data_ptr(), inv_pos.data_ptr(),
+                                    _ptr(topk_w), row_token.numel(), k, x.shape[1], x.stride(0), _dta(x), _stream()),
+          "spd_moe_gather_scaled")
+    return out
+
+
+def moe_combine_gated(y: torch.Tensor, inv_pos: torch.Tensor, tokens: int, top_k: int,
+                      topk_w: Optional[torch.Tensor] = None, shared: Optional[torch.Tensor] = None,
+                      shared_gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Σ_j [w_j] y[row(t, j)] + [sigmoid(shared_gate[t])] shared[t]; shared_gate is an fp32 column
+    (any row stride)."""
+    _cuda(y, inv_pos, topk_w, shared, shared_gate)
+    out = torch.empty((tokens, y.shape[1]), device=y.device, dtype=y.dtype)
+    gs = shared_gate.stride(0) if shared_gate is not None else 0
+    if shared_gate is not None and shared_gate.dtype != torch.float32:
+        raise RuntimeError("moe_combine_gated: the shared gate logits are fp32")
+    check(lib.spd_moe_combine_gated(out.data_ptr(), y.data_ptr(), inv_pos.data_ptr(), _ptr(topk_w), _ptr(shared),
+                                    _ptr(shared_gate), gs, tokens, top_k, y.shape[1], _dta(y), _stream()),
+          "spd_moe_combine_gated")
+    return out
+
+
+def kv_store(key: torch.Tensor, value: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
+             loc: torch.Tensor) -> None:
+    """k_pool[loc] = key rows, v_pool[loc] = value rows (row sizes may differ; any dtype)."""
+    _cuda(key, value, k_pool, v_pool, loc)
+    T = key.shape[0]
+    if T == 0:
+        return
+    k2, v2 = key.reshape(T, -1), value.reshape(T, -1)  # views for row-strided slices of a merged projection
+    if k2.dim() != 2 or v2.dim() != 2 or k2.stride(1) != 1 or v2.stride(1) != 1:
+        raise RuntimeError("kv_store: key / value must be [T, row] with contiguous rows")
+    if loc.dtype != torch.int64:
+        loc = loc.long()
+    check(lib.spd_kv_store(k2.data_ptr(), v2.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), loc.data_ptr(), T,
+                           k2.shape[1], v2.shape[1], k2.stride(0), v2.stride(0), _dta(key), _stream()), "spd_kv_store")
+
+
+def attn_general(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, req_to_token, req_pool_indices,
+                 num_q_heads: int, num_kv_heads: int, head_dim: int, v_dim: int, sm_scale: float, window: int = -1,
+                 sinks: Optional[torch.Tensor] = None, slopes: Optional[torch.Tensor] = None, qtemp_coef: float = 0.0,
+                 qtemp_every: int = 0, seq_lens=None, prefix_lens=None, extend_lens=None, extend_start_loc=None
+                 ) -> torch.Tensor:
+    """Windowed / sink / distance-biased softmax attention over the paged pool; decode (seq_lens) or
+    ragged extend (prefix_lens, extend_lens, extend_start_loc).  q [T, H·head_dim] → [T, H·v_dim]."""
+    _cuda(q, k_pool, v_pool, req_to_token, req_pool_indices, sinks, slopes)
+    T = q.shape[0]
+    if q.dim() != 2 or q.stride(1) != 1:
+        raise RuntimeError("attn_general: q must be [T, H * head_dim] with contiguous rows")
+    if req_pool_indices.dtype != torch.int64 or (seq_lens is not None and seq_lens.dtype != torch.int64):
+        raise RuntimeError("attn_general: req_pool_indices and seq_lens must be int64")
+    for t in (prefix_lens, extend_lens, extend_start_loc):
+        if t is not None and t.dtype != torch.int32:
+            raise RuntimeError("attn_general: prefix_lens / extend_lens / extend_start_loc must be int32")
+    for t in (sinks, slopes):
+        if t is not None and t.dtype != torch.float32:
+            raise RuntimeError("attn_general: sinks and slopes are fp32")
+    out = torch.empty((T, num_q_heads * v_dim), device=q.device, dtype=q.dtype)
+    check(lib.spd_attn_general(out.data_ptr(), q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
+                               req_to_token.data_ptr(), req_pool_indices.data_ptr(), _ptr(seq_lens), _ptr(prefix_lens),
+                               _ptr(extend_lens), _ptr(extend_start_loc), req_pool_indices.numel(), T, num_q_heads,
+                               num_kv_heads, head_dim, v_dim, q.stride(0), out.stride(0), req_to_token.stride(0),
+                               float(sm_scale), int(window), _ptr(sinks), _ptr(slopes), float(qtemp_coef),
+                               int(qtemp_every), _dta(q), _stream()), "spd_attn_general")
+    return out
+
+
+def retention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.Tensor, req_pool_indices,
+              num_heads: int, head_dim: int, v_dim: int, decay: torch.Tensor, cos_sin: Optional[torch.Tensor],
+              rot_dims: int, k_scale: float, seq_lens=None, out_cache_loc=None, prefix_lens=None, extend_lens=None,
+              extend_start_loc=None) -> torch.Tensor:
+    """Decayed linear attention over the per-request recurrent state (updated in place);
+    q / k [T, H·head_dim], v [T, H·v_dim] (row-strided views allowed) → o fp32 [T, H·v_dim]."""
+    _cuda(q, k, v, state, req_pool_indices, decay, cos_sin)
+    T = q.shape[0]
+    if state.dtype != torch.float32 or decay.dtype != torch.float32 or not state.is_contiguous():
+        raise RuntimeError("retention: state and decay are fp32")
+    if any(t.stride(1) != 1 for t in (q, k, v)) or not (q.dtype == k.dtype == v.dtype):
+        raise RuntimeError("retention: q / k / v need contiguous rows and one dtype")
+    o = torch.empty((T, num_heads * v_dim), device=q.device, dtype=torch.float32)
+    check(lib.spd_retention(o.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), state.data_ptr(),
+                            req_pool_indices.data_ptr(), _ptr(seq_lens), _ptr(out_cache_loc), _ptr(prefix_lens),
+                            _ptr(extend_lens), _ptr(extend_start_loc), req_pool_indices.numel(), num_heads, head_dim,
+                            v_dim, q.stride(0), k.stride(0), v.stride(0), decay.data_ptr(), _ptr(cos_sin), int(rot_dims),
+                            cos_sin.shape[0] if cos_sin is not None else 0, float(k_scale), _dta(q), _stream()),
+          "spd_retention")
+    return o
 
 
 # ------------------------------------------------------------------------------------------------

@@ -289,7 +289,8 @@ class ScheduleBatch:
             extend_seq_lens=self.extend_lens if extend else None,
             extend_prefix_lens=self.prefix_lens if extend else None,
             extend_logprob_start_lens=[0] * len(self.reqs) if extend else None,
-            gather_logits=getattr(self, "gather_logits", True))
+            gather_logits=getattr(self, "gather_logits", True),
+            extend_logit_rows=getattr(self, "extend_logit_rows", None) if extend else None)
 
 
 def _cumsum(xs):
