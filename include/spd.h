@@ -156,8 +156,9 @@ int spd_bias_act_residual(void* out, const void* x, const void* bias, const void
  * GEMM — C[M,N] = A[M,K] * W[N,K]^T, 16-bit inputs, fp32 accumulation in TMEM (tcgen05 + TMA).
  * replaces UnquantizedLinearMethod.apply = F.linear (S/layers/linear.py:165-172) for
  * W_qkv / W_o / W_gate_up / W_down and the lm_head matmul (S/layers/logits_processor.py:416-419).
- * lda/ldw/ldc are row strides in elements.  out_f32 != 0: C is fp32 holding the dtype-rounded
- * result (== `.float()` of the 16-bit product, logits_processor.py:440).
+ * lda/ldw/ldc are row strides in elements.  out_f32 == 1: C is fp32 holding the dtype-rounded
+ * result (== `.float()` of the 16-bit product, logits_processor.py:440); out_f32 == 2: C is the
+ * fp32 accumulator itself (routers and logits of models that want them in 32-bit).
  * epilogue: SPD_EPI_NONE, or SPD_EPI_SILU_MUL: W is [2N, K] (gate rows || up rows, the
  * MergedColumnParallelLinear order, S/models/llama.py:67-73) and C[M,N] = silu(A Wg^T) * (A Wu^T),
  * both products rounded to dtype first (== gate_up_proj followed by SiluAndMul).

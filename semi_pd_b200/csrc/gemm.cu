@@ -330,10 +330,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUt
             for (int j = 0; j < kChunk; j += 4) {
               if (nl + j < p.y_rows) {
                 float4 o;
-                o.x = to_f32<T>(from_f32<T>(v[j]));
-                o.y = to_f32<T>(from_f32<T>(v[j + 1]));
-                o.z = to_f32<T>(from_f32<T>(v[j + 2]));
-                o.w = to_f32<T>(from_f32<T>(v[j + 3]));
+                o.x = f32_result<T>(v[j], p.out_f32);
+                o.y = f32_result<T>(v[j + 1], p.out_f32);
+                o.z = f32_result<T>(v[j + 2], p.out_f32);
+                o.w = f32_result<T>(v[j + 3], p.out_f32);
                 *reinterpret_cast<float4*>(dst + j) = o;
               }
             }
@@ -364,7 +364,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUt
             float* dst = reinterpret_cast<float*>(p.C) + static_cast<int64_t>(m0) * p.ldc + nn;
 #pragma unroll
             for (int j = 0; j < kChunk; ++j)
-              if (j < m_left) dst[static_cast<int64_t>(j) * p.ldc] = to_f32<T>(from_f32<T>(v[j]));
+              if (j < m_left) dst[static_cast<int64_t>(j) * p.ldc] = f32_result<T>(v[j], p.out_f32);
           } else {
             T* dst = reinterpret_cast<T*>(p.C) + static_cast<int64_t>(m0) * p.ldc + nn;
 #pragma unroll

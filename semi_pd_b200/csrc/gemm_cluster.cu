@@ -194,7 +194,7 @@ gemm_cluster_splitk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid
             float* dst = reinterpret_cast<float*>(p.C) + static_cast<int64_t>(c) * p.ldc + nn;
 #pragma unroll
             for (int j = 0; j < kChunk; ++j)
-              if (j < m_left) dst[static_cast<int64_t>(j) * p.ldc] = to_f32<T>(from_f32<T>(v[j]));
+              if (j < m_left) dst[static_cast<int64_t>(j) * p.ldc] = f32_result<T>(v[j], p.out_f32);
           } else {
             T* dst = reinterpret_cast<T*>(p.C) + static_cast<int64_t>(c) * p.ldc + nn;
 #pragma unroll

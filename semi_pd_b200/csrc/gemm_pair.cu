@@ -245,10 +245,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             for (int j = 0; j < 32; j += 4) {
               if (n0 + j < p.n_cols) {
                 float4 o;
-                o.x = to_f32<T>(from_f32<T>(v[j]));
-                o.y = to_f32<T>(from_f32<T>(v[j + 1]));
-                o.z = to_f32<T>(from_f32<T>(v[j + 2]));
-                o.w = to_f32<T>(from_f32<T>(v[j + 3]));
+                o.x = f32_result<T>(v[j], p.out_f32);
+                o.y = f32_result<T>(v[j + 1], p.out_f32);
+                o.z = f32_result<T>(v[j + 2], p.out_f32);
+                o.w = f32_result<T>(v[j + 3], p.out_f32);
                 *reinterpret_cast<float4*>(dst + j) = o;
               }
             }

@@ -301,7 +301,7 @@ gemm_pair_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_co
       OutT* st = reinterpret_cast<OutT*>(sOut);
 #pragma unroll
       for (int j = 0; j < kChunk; ++j) {
-        if constexpr (sizeof(OutT) == 4) st[j * kPdBM + row] = to_f32<T>(from_f32<T>(v[j]));
+        if constexpr (sizeof(OutT) == 4) st[j * kPdBM + row] = f32_result<T>(v[j], p.out_f32);
         else st[j * kPdBM + row] = from_f32<T>(v[j]);
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");

@@ -313,8 +313,9 @@ def _gemm_workspace(device: torch.device) -> torch.Tensor:
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None,
-           out_f32: bool = False, epilogue: int = SPD_EPI_NONE) -> torch.Tensor:
-    """F.linear(x, weight) — x [M, K], weight [N, K] (or [2N, K] with SPD_EPI_SILU_MUL)."""
+           out_f32: bool = False, epilogue: int = SPD_EPI_NONE, exact_f32: bool = False) -> torch.Tensor:
+    """F.linear(x, weight) — x [M, K], weight [N, K] (or [2N, K] with SPD_EPI_SILU_MUL).  out_f32:
+    the 16-bit product as fp32 (`.float()` of a 16-bit matmul); with exact_f32 the fp32 accumulator."""
     _cuda(x, weight)
     if x.dim() != 2 or weight.dim() != 2 or x.stride(1) != 1 or weight.stride(1) != 1:
         raise RuntimeError("linear: x and weight must be 2-D with contiguous last dimension")
@@ -328,7 +329,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = 
         out = torch.empty((M, N), device=x.device, dtype=torch.float32 if out_f32 else x.dtype)
     ws = _gemm_workspace(x.device)
     check(lib.spd_gemm(out.data_ptr(), x.data_ptr(), weight.data_ptr(), M, N, K, x.stride(0),
-                       weight.stride(0), out.stride(0), _dt(x), 1 if out_f32 else 0, epilogue,
+                       weight.stride(0), out.stride(0), _dt(x), (2 if exact_f32 else 1) if out_f32 else 0, epilogue,
                        ws.data_ptr(), ws.numel(), get_sm_budget(), _stream()), "spd_gemm")
     return out
 
@@ -615,7 +616,7 @@ def linear_any(x: torch.Tensor, weight: torch.Tensor, out_f32: bool = False) -> 
     """F.linear for the hybrid family: the tcgen05 GEMMs where they apply (16-bit, aligned shapes),
     the CUDA-core GEMM otherwise (float32 models, odd sizes)."""
     if _tc_gemm_ok(x, weight, weight.shape[0]) and os.environ.get("SPD_HYBRID_GEMM", "tc") == "tc":
-        return linear(x, weight, out_f32=out_f32)
+        return linear(x, weight, out_f32=out_f32, exact_f32=True)
     return linear_simt(x, weight, out_f32=out_f32)
 
 
