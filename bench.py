@@ -75,6 +75,10 @@ def parse_args():
     ap.add_argument("--no-roofline", action="store_true")
     ap.add_argument("--tp-steps", type=int, default=3)
     ap.add_argument("--clocks-csv", type=str, default="", help="write the nvidia-smi samples of the run here")
+    ap.add_argument("--family", type=str, default="", choices=["", "rimidra"],
+                    help="instead of the default workload: prefill / decode throughput and per-kernel rooflines of "
+                         "that model family beside Llama at equal size (scripts/bench_rimidra.py)")
+    ap.add_argument("--family-sizes", type=str, default="s,m")
     return ap.parse_args()
 
 
@@ -577,6 +581,12 @@ def tp_arm(args, model_name, rank, world, local_rank, dtype, requests, steps, ta
 # ----------------------------------------------------------------------------------------------
 def main():
     args = parse_args()
+    if args.family:
+        sys.path.insert(0, os.path.join(ROOT, "scripts"))
+        import bench_rimidra
+        res = bench_rimidra.run(tuple(args.family_sizes.split(",")))
+        print(json.dumps({"family": args.family, "data": "synthetic", "dtype": "bf16", **res}))
+        return
     rank = int(os.environ.get("RANK", 0))
     local_rank = int(os.environ.get("LOCAL_RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))

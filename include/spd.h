@@ -393,14 +393,16 @@ int spd_kv_store(const void* k, const void* v, void* k_pool, void* v_pool, const
  * window (window <= 0: all j <= i).  score = (q . k) * sm_scale * temp(i) - slopes[h] * (i - j) with
  * temp(i) = 1 + qtemp_coef * ln(floor((i + 1) / qtemp_every) + 1) (qtemp_every <= 0: 1); slopes nullable.
  * sinks != NULL: exp(sinks[h]) joins the softmax denominator.  key size head_dim, value size v_dim;
- * k_pool [slots, kv_heads, head_dim], v_pool [slots, kv_heads, v_dim]; out [tokens, heads * v_dim]. */
+ * k_pool [slots, kv_heads, head_dim], v_pool [slots, kv_heads, v_dim]; out [tokens, heads * v_dim].
+ * max_extend_len (extend): an upper bound of extend_lens known on the host; > 0 lets 16-bit prefill
+ * take the tensor-core kernel (64-row query tiles), 0 keeps the CUDA-core kernel. */
 int spd_attn_general(void* out, const void* q, const void* k_pool, const void* v_pool,
                      const int32_t* req_to_token, const int64_t* req_pool_indices, const int64_t* seq_lens,
                      const int32_t* prefix_lens, const int32_t* extend_lens, const int32_t* extend_start_loc,
                      int64_t batch, int64_t total_tokens, int num_q_heads, int num_kv_heads, int head_dim,
                      int v_dim, int64_t q_stride, int64_t out_stride, int64_t req_to_token_stride,
                      float sm_scale, int window, const float* sinks, const float* slopes, float qtemp_coef,
-                     int qtemp_every, int dtype, spd_stream_t stream);
+                     int qtemp_every, int64_t max_extend_len, int dtype, spd_stream_t stream);
 /* Retention (linear attention with a fixed per-head decay, no softmax): per head
  *   S_t = decay[h] S_(t-1) + k_t v_t^T,  o_t = S_t^T q_t
  * with q, k rotated over their first rot_dims dimensions (rotate-half pairing, cos_sin [positions,

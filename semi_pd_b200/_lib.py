@@ -101,7 +101,7 @@ SIGNATURES = {
     "spd_attn_general": (
         _i,
         [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i, _i, _i, _i, _i64, _i64, _i64, _f, _i, _p, _p,
-         _f, _i, _i, _p],
+         _f, _i, _i64, _i, _p],
     ),
     "spd_retention": (
         _i,

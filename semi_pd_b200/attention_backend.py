@@ -174,7 +174,8 @@ class SpdAttnBackend(AttentionBackend):
                                     seq_lens=forward_batch.seq_lens, **common)
         return ops.attn_general(q, k_buf, v_buf, r2t, forward_batch.req_pool_indices,
                                 prefix_lens=forward_batch.extend_prefix_lens, extend_lens=forward_batch.extend_seq_lens,
-                                extend_start_loc=forward_batch.extend_start_loc, **common)
+                                extend_start_loc=forward_batch.extend_start_loc, max_extend_len=self.max_extend_len,
+                                **common)
 
     def forward_retention(self, q, k, v, layer, forward_batch: ForwardBatch):
         """Retention mixer (decayed linear attention) over the request's recurrent state slot;

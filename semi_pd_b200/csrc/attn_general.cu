@@ -141,6 +141,100 @@ attn_general_kernel(T* __restrict__ out, const T* __restrict__ q, const T* __res
   }
 }
 
+// Decode: one CTA per (request, query head); its four warps take the key tiles of the window in turn
+// (tile i goes to warp i mod 4) and their partial (max, sum, output) triples are merged through shared
+// memory by warp 0 — four times the loads in flight per (request, head) of the one-warp form.
+template <typename T>
+__global__ void __launch_bounds__(128)
+attn_general_decode_kernel(T* __restrict__ out, const T* __restrict__ q, const T* __restrict__ k_pool,
+                           const T* __restrict__ v_pool, const int32_t* __restrict__ req_to_token,
+                           const int64_t* __restrict__ req_pool_indices, const int64_t* __restrict__ seq_lens, int H,
+                           int G, int dk, int dv, int64_t q_stride, int64_t out_stride, int64_t r2t_stride,
+                           float sm_scale, int window, const float* __restrict__ sinks,
+                           const float* __restrict__ slopes, float qtemp_coef, int qtemp_every) {
+  griddep_wait();
+  griddep_launch_dependents();
+  extern __shared__ float dec_smem[];  // q [dk] | m [4] | l [4] | acc [4][dv]
+  float* qs = dec_smem;
+  float* sm_m = qs + dk;
+  float* sm_l = sm_m + 4;
+  float* sm_acc = sm_l + 4;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int r = blockIdx.x, h = blockIdx.y;
+  const int64_t pos = seq_lens[r] - 1;
+  if (pos < 0) return;
+  const int32_t* page = req_to_token + req_pool_indices[r] * r2t_stride;
+  const int g = h / (H / G);
+  float temp = 1.f;
+  if (qtemp_every > 0) temp = 1.f + qtemp_coef * logf((float)((pos + 1) / qtemp_every + 1));
+  const float qmul = sm_scale * temp;
+  for (int d = threadIdx.x; d < dk; d += 128) qs[d] = to_f32<T>(q[(int64_t)r * q_stride + (int64_t)h * dk + d]) * qmul;
+  __syncthreads();
+  const float slope = slopes != nullptr ? slopes[h] : 0.f;
+  float m = -INFINITY, l = 0.f;
+  float acc[kGenMaxVPerLane];
+#pragma unroll
+  for (int i = 0; i < kGenMaxVPerLane; ++i) acc[i] = 0.f;
+  const int64_t j_lo = window > 0 ? (pos - window + 1 > 0 ? pos - window + 1 : 0) : 0;
+  for (int64_t j0 = j_lo + 32 * warp; j0 <= pos; j0 += 128) {
+    const int64_t j = j0 + lane;
+    const bool valid = j <= pos;
+    int slot = 0;
+    float s = -INFINITY;
+    if (valid) {
+      slot = page[j];
+      s = dot_row<T>(qs, k_pool + ((int64_t)slot * G + g) * dk, dk) - slope * (float)(pos - j);
+    }
+    const float m_new = fmaxf(m, warp_max(s));
+    const float corr = expf(m - m_new);
+    const float p = valid ? expf(s - m_new) : 0.f;
+    l = l * corr + warp_sum(p);
+    m = m_new;
+#pragma unroll
+    for (int i = 0; i < kGenMaxVPerLane; ++i) acc[i] *= corr;
+    const int n = (int)(pos - j0 + 1 < 32 ? pos - j0 + 1 : 32);
+    for (int jj = 0; jj < n; ++jj) {
+      const float pj = __shfl_sync(0xffffffffu, p, jj);
+      const int sj = __shfl_sync(0xffffffffu, slot, jj);
+      const T* vrow = v_pool + ((int64_t)sj * G + g) * dv;
+#pragma unroll
+      for (int i = 0; i < kGenMaxVPerLane; ++i) {
+        const int c = lane + 32 * i;
+        if (c < dv) acc[i] = fmaf(pj, to_f32<T>(vrow[c]), acc[i]);
+      }
+    }
+  }
+  if (lane == 0) { sm_m[warp] = m; sm_l[warp] = l; }
+#pragma unroll
+  for (int i = 0; i < kGenMaxVPerLane; ++i) {
+    const int c = lane + 32 * i;
+    if (c < dv) sm_acc[warp * dv + c] = acc[i];
+  }
+  __syncthreads();
+  if (warp != 0) return;
+  float mt = sinks != nullptr ? sinks[h] : -INFINITY;
+#pragma unroll
+  for (int w = 0; w < 4; ++w) mt = fmaxf(mt, sm_m[w]);
+  float lt = sinks != nullptr ? expf(sinks[h] - mt) : 0.f;
+  float f[4];
+#pragma unroll
+  for (int w = 0; w < 4; ++w) {
+    f[w] = sm_m[w] == -INFINITY ? 0.f : expf(sm_m[w] - mt);  // a warp without keys contributes nothing
+    lt += sm_l[w] * f[w];
+  }
+  const float inv = 1.0f / lt;
+#pragma unroll
+  for (int i = 0; i < kGenMaxVPerLane; ++i) {
+    const int c = lane + 32 * i;
+    if (c < dv) {
+      float v = 0.f;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) v += sm_acc[w * dv + c] * f[w];
+      out[(int64_t)r * out_stride + (int64_t)h * dv + c] = from_f32<T>(v * inv);
+    }
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 kv_store_kernel(const T* __restrict__ k, const T* __restrict__ v, T* __restrict__ k_pool, T* __restrict__ v_pool,
@@ -153,6 +247,13 @@ kv_store_kernel(const T* __restrict__ k, const T* __restrict__ v, T* __restrict_
   if (v != nullptr)
     for (int64_t i = threadIdx.x; i < v_row; i += 256) v_pool[slot * v_row + i] = v[t * v_stride + i];
 }
+
+int attn_general_mma_try(void* out, const void* q, const void* k_pool, const void* v_pool, const int32_t* req_to_token,
+                         const int64_t* req_pool_indices, const int32_t* prefix_lens, const int32_t* extend_lens,
+                         const int32_t* extend_start_loc, int64_t batch, int64_t max_extend_len, int H, int G, int dk,
+                         int dv, int64_t q_stride, int64_t out_stride, int64_t r2t_stride, float sm_scale, int window,
+                         const float* sinks, const float* slopes, float qtemp_coef, int qtemp_every, int dtype,
+                         cudaStream_t stream);
 
 }  // namespace spd
 
@@ -180,7 +281,7 @@ int spd_attn_general(void* out, const void* q, const void* k_pool, const void* v
                      int64_t batch, int64_t total_tokens, int num_q_heads, int num_kv_heads, int head_dim,
                      int v_dim, int64_t q_stride, int64_t out_stride, int64_t req_to_token_stride,
                      float sm_scale, int window, const float* sinks, const float* slopes, float qtemp_coef,
-                     int qtemp_every, int dtype, spd_stream_t stream) {
+                     int qtemp_every, int64_t max_extend_len, int dtype, spd_stream_t stream) {
   SPD_REQUIRE(out && q && k_pool && v_pool && req_to_token && req_pool_indices, SPD_E_BADARG,
               "spd_attn_general: null pointer");
   SPD_REQUIRE(seq_lens != nullptr || (prefix_lens && extend_lens && extend_start_loc), SPD_E_BADARG,
@@ -191,6 +292,24 @@ int spd_attn_general(void* out, const void* q, const void* k_pool, const void* v
               "spd_attn_general: head_dim %d / v_dim %d above %d", head_dim, v_dim, kGenMaxHeadDim);
   SPD_REQUIRE(seq_lens == nullptr || batch == total_tokens, SPD_E_BADARG, "spd_attn_general: decode has one row per request");
   if (total_tokens == 0 || batch == 0) return 0;
+  if (seq_lens != nullptr) {
+    SPD_REQUIRE(batch < (1ll << 31) && num_q_heads <= 65535, SPD_E_SHAPE, "spd_attn_general: batch too large");
+    const size_t dsmem = sizeof(float) * ((size_t)head_dim + 8 + 4 * (size_t)v_dim);
+    SPD_DISPATCH_ANY(dtype, {
+      SPD_CUDA(launch(attn_general_decode_kernel<T>, dim3((unsigned)batch, (unsigned)num_q_heads), dim3(128), dsmem,
+                      as_stream(stream), pdl_enabled(), (T*)out, (const T*)q, (const T*)k_pool, (const T*)v_pool,
+                      req_to_token, req_pool_indices, seq_lens, num_q_heads, num_kv_heads, head_dim, v_dim, q_stride,
+                      out_stride, req_to_token_stride, sm_scale, window, sinks, slopes, qtemp_coef, qtemp_every));
+    });
+    return 0;
+  }
+  if (max_extend_len > 0) {  // 16-bit prefill on the tensor cores where the head sizes are instantiated
+    const int rc = attn_general_mma_try(out, q, k_pool, v_pool, req_to_token, req_pool_indices, prefix_lens, extend_lens,
+                                        extend_start_loc, batch, max_extend_len, num_q_heads, num_kv_heads, head_dim,
+                                        v_dim, q_stride, out_stride, req_to_token_stride, sm_scale, window, sinks, slopes,
+                                        qtemp_coef, qtemp_every, dtype, as_stream(stream));
+    if (rc != 1) return rc;
+  }
   const int64_t tokens4 = (total_tokens + 3) / 4 * 4;
   const int64_t ctas = tokens4 / 4 * num_q_heads;
   SPD_REQUIRE(ctas < (1ll << 31), SPD_E_SHAPE, "spd_attn_general: batch too large");

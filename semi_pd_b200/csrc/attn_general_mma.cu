@@ -1,0 +1,267 @@
+// Tensor-core prefill path of the general attention (window, sink, distance bias, query temperature,
+// key size != value size) for 16-bit models: a CTA owns 64 consecutive query rows of one request and
+// one query head, its four warps 16 rows each; K / V tiles of 64 keys are gathered through the page
+// table with 16-byte cp.async into a double-buffered shared-memory ring, S = Q K^T and O += P V run
+// on warp-level mma.sync.m16n8k16 (fp32 accumulators), and the online softmax — scale, temperature,
+// bias, window mask, sink — is fp32 in the exp2 domain.  Only the keys a tile can see are visited:
+// [first row - window + 1, last row].  The CUDA-core kernel of attn_general.cu keeps decode, float32
+// models and head sizes outside the instantiated set.  (mma.sync, not tcgen05: the first tensor-core
+// kernel of this mechanism.)
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace spd {
+
+constexpr int kGmBQ = 64, kGmBK = 64, kGmThreads = 128;
+constexpr float kLog2e = 1.4426950408889634f;
+
+template <typename T>
+__device__ __forceinline__ void gm_mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1);
+template <>
+__device__ __forceinline__ void gm_mma<__nv_bfloat16>(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <>
+__device__ __forceinline__ void gm_mma<__half>(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void gm_ldsm_x4(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void gm_ldsm_x4_trans(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(smem_u32(p)));
+}
+
+template <typename T, int DK, int DV>
+__global__ void __launch_bounds__(kGmThreads)
+attn_general_mma_kernel(T* __restrict__ out, const T* __restrict__ q, const T* __restrict__ k_pool,
+                        const T* __restrict__ v_pool, const int32_t* __restrict__ req_to_token,
+                        const int64_t* __restrict__ req_pool_indices, const int32_t* __restrict__ prefix_lens,
+                        const int32_t* __restrict__ extend_lens, const int32_t* __restrict__ extend_start_loc, int H,
+                        int G, int64_t q_stride, int64_t out_stride, int64_t r2t_stride, float sm_scale, int window,
+                        const float* __restrict__ sinks, const float* __restrict__ slopes, float qtemp_coef,
+                        int qtemp_every) {
+  constexpr int LDK = DK + 8, LDV = DV + 8;  // +16 B per row: ldmatrix rows fall into distinct banks
+  extern __shared__ __align__(16) unsigned char gm_smem[];
+  T* sQ = reinterpret_cast<T*>(gm_smem);   // [BQ][LDK]
+  T* sK = sQ + kGmBQ * LDK;                // [2][BK][LDK]
+  T* sV = sK + 2 * kGmBK * LDK;            // [2][BK][LDV]
+  griddep_wait();
+  griddep_launch_dependents();
+  const int r = blockIdx.y, h = blockIdx.z;
+  const int ext = extend_lens[r];
+  const int q0 = blockIdx.x * kGmBQ;
+  if (q0 >= ext) return;
+  const int nq = ext - q0 < kGmBQ ? ext - q0 : kGmBQ;
+  const int64_t i0 = (int64_t)prefix_lens[r] + q0;        // position of the tile's first query
+  const int64_t row0 = (int64_t)extend_start_loc[r] + q0;  // its row in q / out
+  const int32_t* page = req_to_token + req_pool_indices[r] * r2t_stride;
+  const int g = h / (H / G);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+  for (int idx = tid; idx < kGmBQ * (DK / 8); idx += kGmThreads) {
+    const int row = idx / (DK / 8), c = idx % (DK / 8);
+    const bool ok = row < nq;
+    cp_async16(smem_u32(sQ + row * LDK + c * 8), q + (row0 + (ok ? row : 0)) * q_stride + (int64_t)h * DK + c * 8, ok);
+  }
+  const int64_t j_hi = i0 + nq - 1;
+  const int64_t j_lo = window > 0 ? (i0 - window + 1 > 0 ? i0 - window + 1 : 0) : 0;
+  const int ntiles = (int)((j_hi - j_lo) / kGmBK) + 1;
+  auto load_kv = [&](int t, int buf) {
+    const int64_t jb = j_lo + (int64_t)t * kGmBK;
+    for (int idx = tid; idx < kGmBK * (DK / 8); idx += kGmThreads) {
+      const int row = idx / (DK / 8), c = idx % (DK / 8);
+      const bool ok = jb + row <= j_hi;
+      const int64_t slot = ok ? page[jb + row] : 0;
+      cp_async16(smem_u32(sK + (buf * kGmBK + row) * LDK + c * 8), k_pool + (slot * G + g) * DK + c * 8, ok);
+    }
+    for (int idx = tid; idx < kGmBK * (DV / 8); idx += kGmThreads) {
+      const int row = idx / (DV / 8), c = idx % (DV / 8);
+      const bool ok = jb + row <= j_hi;
+      const int64_t slot = ok ? page[jb + row] : 0;
+      cp_async16(smem_u32(sV + (buf * kGmBK + row) * LDV + c * 8), v_pool + (slot * G + g) * DV + c * 8, ok);
+    }
+  };
+  load_kv(0, 0);
+  cp_async_commit();
+
+  const int rl[2] = {warp * 16 + (lane >> 2), warp * 16 + (lane >> 2) + 8};
+  const int64_t pi[2] = {i0 + rl[0], i0 + rl[1]};
+  float sc[2];
+#pragma unroll
+  for (int x = 0; x < 2; ++x) {
+    float temp = 1.f;
+    if (qtemp_every > 0) temp = 1.f + qtemp_coef * logf((float)((pi[x] + 1) / qtemp_every + 1));
+    sc[x] = sm_scale * temp * kLog2e;
+  }
+  const float sl = (slopes != nullptr ? slopes[h] : 0.f) * kLog2e;
+  const float sink2 = sinks != nullptr ? sinks[h] * kLog2e : -INFINITY;
+  float m[2] = {sink2, sink2}, l[2] = {0.f, 0.f};  // l: this thread's share of the row sum
+  float o[DV / 8][4];
+#pragma unroll
+  for (int i = 0; i < DV / 8; ++i)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[i][e] = 0.f;
+
+  for (int t = 0; t < ntiles; ++t) {
+    const int buf = t & 1;
+    if (t + 1 < ntiles) {
+      load_kv(t + 1, buf ^ 1);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    float s[kGmBK / 8][4];
+#pragma unroll
+    for (int i = 0; i < kGmBK / 8; ++i)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s[i][e] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < DK / 16; ++kk) {
+      uint32_t a[4];
+      gm_ldsm_x4(a, sQ + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDK + kk * 16 + (lane >> 4) * 8);
+#pragma unroll
+      for (int nb2 = 0; nb2 < kGmBK / 16; ++nb2) {
+        uint32_t b[4];
+        gm_ldsm_x4(b, sK + (buf * kGmBK + nb2 * 16 + (lane & 7) + (lane >> 4) * 8) * LDK + kk * 16 + ((lane >> 3) & 1) * 8);
+        gm_mma<T>(s[2 * nb2], a, b[0], b[1]);
+        gm_mma<T>(s[2 * nb2 + 1], a, b[2], b[3]);
+      }
+    }
+    const int64_t jb = j_lo + (int64_t)t * kGmBK;
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nb = 0; nb < kGmBK / 8; ++nb)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int x = e >> 1;
+        const int64_t j = jb + nb * 8 + (lane & 3) * 2 + (e & 1);
+        const int64_t dist = pi[x] - j;
+        const bool ok = dist >= 0 && (window <= 0 || dist < window) && pi[x] <= j_hi;
+        const float v = ok ? s[nb][e] * sc[x] - sl * (float)dist : -INFINITY;
+        s[nb][e] = v;
+        mx[x] = fmaxf(mx[x], v);
+      }
+    float ms[2];
+#pragma unroll
+    for (int x = 0; x < 2; ++x) {
+      mx[x] = fmaxf(mx[x], __shfl_xor_sync(0xffffffffu, mx[x], 1));
+      mx[x] = fmaxf(mx[x], __shfl_xor_sync(0xffffffffu, mx[x], 2));
+      const float m_new = fmaxf(m[x], mx[x]);
+      ms[x] = m_new == -INFINITY ? 0.f : m_new;
+      const float corr = exp2f(m[x] - ms[x]);  // m = -inf: 0 (nothing accumulated yet)
+      m[x] = m_new;
+      l[x] *= corr;
+#pragma unroll
+      for (int i = 0; i < DV / 8; ++i) {
+        o[i][2 * x] *= corr;
+        o[i][2 * x + 1] *= corr;
+      }
+    }
+#pragma unroll
+    for (int nb = 0; nb < kGmBK / 8; ++nb)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float p = exp2f(s[nb][e] - ms[e >> 1]);
+        s[nb][e] = p;
+        l[e >> 1] += p;
+      }
+#pragma unroll
+    for (int kk = 0; kk < kGmBK / 16; ++kk) {
+      uint32_t a[4];
+      a[0] = pack2<T>(s[2 * kk][0], s[2 * kk][1]);
+      a[1] = pack2<T>(s[2 * kk][2], s[2 * kk][3]);
+      a[2] = pack2<T>(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+      a[3] = pack2<T>(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+      for (int nb2 = 0; nb2 < DV / 16; ++nb2) {
+        uint32_t b[4];
+        gm_ldsm_x4_trans(b, sV + (buf * kGmBK + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDV + nb2 * 16 + (lane >> 4) * 8);
+        gm_mma<T>(o[2 * nb2], a, b[0], b[1]);
+        gm_mma<T>(o[2 * nb2 + 1], a, b[2], b[3]);
+      }
+    }
+    __syncthreads();  // the next iteration's prefetch overwrites the buffer just read
+  }
+#pragma unroll
+  for (int x = 0; x < 2; ++x) {
+    float sum = l[x];
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    if (sinks != nullptr) sum += exp2f(sink2 - m[x]);
+    if (rl[x] < nq) {
+      const float inv = 1.0f / sum;
+      T* dst = out + (row0 + rl[x]) * out_stride + (int64_t)h * DV + (lane & 3) * 2;
+#pragma unroll
+      for (int nb = 0; nb < DV / 8; ++nb)
+        *reinterpret_cast<uint32_t*>(dst + nb * 8) = pack2<T>(o[nb][2 * x] * inv, o[nb][2 * x + 1] * inv);
+    }
+  }
+}
+
+template <typename T, int DK, int DV>
+static int gm_launch(void* out, const void* q, const void* k_pool, const void* v_pool, const int32_t* req_to_token,
+                     const int64_t* req_pool_indices, const int32_t* prefix_lens, const int32_t* extend_lens,
+                     const int32_t* extend_start_loc, int64_t batch, int64_t max_extend_len, int H, int G,
+                     int64_t q_stride, int64_t out_stride, int64_t r2t_stride, float sm_scale, int window,
+                     const float* sinks, const float* slopes, float qtemp_coef, int qtemp_every, cudaStream_t stream) {
+  constexpr size_t smem = sizeof(T) * ((size_t)kGmBQ * (DK + 8) + 2 * kGmBK * (DK + 8) + 2 * kGmBK * (DV + 8));
+  static bool configured = false;  // per instantiation
+  if (!configured) {
+    SPD_CUDA(cudaFuncSetAttribute(attn_general_mma_kernel<T, DK, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = true;
+  }
+  const dim3 grid((unsigned)((max_extend_len + kGmBQ - 1) / kGmBQ), (unsigned)batch, (unsigned)H);
+  SPD_CUDA(launch(attn_general_mma_kernel<T, DK, DV>, grid, dim3(kGmThreads), smem, stream, pdl_enabled(), (T*)out,
+                  (const T*)q, (const T*)k_pool, (const T*)v_pool, req_to_token, req_pool_indices, prefix_lens,
+                  extend_lens, extend_start_loc, H, G, q_stride, out_stride, r2t_stride, sm_scale, window, sinks, slopes,
+                  qtemp_coef, qtemp_every));
+  return 0;
+}
+
+// → 0 launched, 1 not applicable (the caller falls back to the CUDA-core kernel), else an error
+int attn_general_mma_try(void* out, const void* q, const void* k_pool, const void* v_pool, const int32_t* req_to_token,
+                         const int64_t* req_pool_indices, const int32_t* prefix_lens, const int32_t* extend_lens,
+                         const int32_t* extend_start_loc, int64_t batch, int64_t max_extend_len, int H, int G, int dk,
+                         int dv, int64_t q_stride, int64_t out_stride, int64_t r2t_stride, float sm_scale, int window,
+                         const float* sinks, const float* slopes, float qtemp_coef, int qtemp_every, int dtype,
+                         cudaStream_t stream) {
+  if (dtype != SPD_BF16 && dtype != SPD_F16) return 1;
+  if (max_extend_len < 16 || batch > 65535 || H > 65535) return 1;  // short portions: the CUDA-core kernel
+  if (q_stride % 8 != 0 || out_stride % 2 != 0 || !aligned16(q) || !aligned16(k_pool) || !aligned16(v_pool) ||
+      (reinterpret_cast<uintptr_t>(out) & 3u) != 0)
+    return 1;
+#define SPD_GM_CASE(DKV, DVV)                                                                                       \
+  if (dk == DKV && dv == DVV) {                                                                                     \
+    if (dtype == SPD_BF16)                                                                                          \
+      return gm_launch<__nv_bfloat16, DKV, DVV>(out, q, k_pool, v_pool, req_to_token, req_pool_indices, prefix_lens, \
+                                                extend_lens, extend_start_loc, batch, max_extend_len, H, G, q_stride, \
+                                                out_stride, r2t_stride, sm_scale, window, sinks, slopes, qtemp_coef, \
+                                                qtemp_every, stream);                                               \
+    return gm_launch<__half, DKV, DVV>(out, q, k_pool, v_pool, req_to_token, req_pool_indices, prefix_lens,        \
+                                       extend_lens, extend_start_loc, batch, max_extend_len, H, G, q_stride,        \
+                                       out_stride, r2t_stride, sm_scale, window, sinks, slopes, qtemp_coef,         \
+                                       qtemp_every, stream);                                                        \
+  }
+  SPD_GM_CASE(32, 32)
+  SPD_GM_CASE(64, 64)
+  SPD_GM_CASE(64, 128)
+  SPD_GM_CASE(128, 64)
+  SPD_GM_CASE(128, 128)
+#undef SPD_GM_CASE
+  return 1;
+}
+
+}  // namespace spd

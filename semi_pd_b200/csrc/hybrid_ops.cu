@@ -69,6 +69,44 @@ embed_f32_kernel(float* __restrict__ x, const T* __restrict__ table, const int64
   for (int64_t i = threadIdx.x; i < dim; i += kRowThreads) x[row * dim + i] = to_f32<T>(table[id * dim + i]);
 }
 
+// 16-byte vectors of T (8 x 16-bit or 4 x float)
+template <typename T>
+struct Vec16 {
+  static constexpr int kN = 16 / sizeof(T);
+  uint4 raw;
+  __device__ __forceinline__ T* e() { return reinterpret_cast<T*>(&raw); }
+  __device__ __forceinline__ const T* e() const { return reinterpret_cast<const T*>(&raw); }
+};
+template <typename T>
+__device__ __forceinline__ Vec16<T> ldv(const T* p) {
+  Vec16<T> v;
+  v.raw = *reinterpret_cast<const uint4*>(p);
+  return v;
+}
+template <typename T>
+__device__ __forceinline__ void stv(T* p, const Vec16<T>& v) { *reinterpret_cast<uint4*>(p) = v.raw; }
+
+// vector form: inter a multiple of the vector width, 16-byte aligned pointers
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads)
+act_and_mul_vec_kernel(T* __restrict__ out, const T* __restrict__ x, int64_t rows, int64_t inter, int act) {
+  griddep_wait();
+  griddep_launch_dependents();
+  constexpr int N = Vec16<T>::kN;
+  const int64_t per_row = inter / N, n = rows * per_row;
+  for (int64_t i = blockIdx.x * (int64_t)kRowThreads + threadIdx.x; i < n; i += (int64_t)gridDim.x * kRowThreads) {
+    const int64_t r = i / per_row, c = (i - r * per_row) * N;
+    const Vec16<T> g = ldv(x + r * 2 * inter + c), u = ldv(x + r * 2 * inter + inter + c);
+    Vec16<T> o;
+#pragma unroll
+    for (int k = 0; k < N; ++k) {
+      const float gv = to_f32<T>(g.e()[k]);
+      o.e()[k] = from_f32<T>((act == 0 ? silu_precise(gv) : gelu_tanh_precise(gv)) * to_f32<T>(u.e()[k]));
+    }
+    stv(out + r * inter + c, o);
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kRowThreads)
 act_and_mul_kernel(T* __restrict__ out, const T* __restrict__ x, int64_t rows, int64_t inter, int act) {
@@ -264,6 +302,21 @@ moe_gather_scaled_kernel(T* __restrict__ xs, const T* __restrict__ x, const int3
     for (int j = 0; j < top_k; ++j)
       if (inv_pos[(int64_t)t * top_k + j] == (int32_t)r) w = topk_w[(int64_t)t * top_k + j];
   }
+  constexpr int N = Vec16<T>::kN;
+  if (dim % N == 0 && x_stride % N == 0 && ((reinterpret_cast<uintptr_t>(xs) | reinterpret_cast<uintptr_t>(x)) & 15u) == 0) {
+    for (int64_t i = threadIdx.x * N; i < dim; i += kRowThreads * N) {
+      Vec16<T> o;
+      if (t < 0) {
+        o.raw = make_uint4(0u, 0u, 0u, 0u);
+      } else {
+        const Vec16<T> v = ldv(x + (int64_t)t * x_stride + i);
+#pragma unroll
+        for (int k = 0; k < N; ++k) o.e()[k] = from_f32<T>(w * to_f32<T>(v.e()[k]));
+      }
+      stv(xs + r * dim + i, o);
+    }
+    return;
+  }
   for (int64_t i = threadIdx.x; i < dim; i += kRowThreads)
     xs[r * dim + i] = t < 0 ? from_f32<T>(0.f) : from_f32<T>(w * to_f32<T>(x[(int64_t)t * x_stride + i]));
 }
@@ -277,6 +330,31 @@ moe_combine_gated_kernel(T* __restrict__ out, const T* __restrict__ y, const int
   griddep_launch_dependents();
   const int64_t t = blockIdx.x;
   const float sg = shared_gate != nullptr ? sigmoid_precise(shared_gate[t * gate_stride]) : 1.f;
+  constexpr int N = Vec16<T>::kN;
+  if (dim % N == 0 && ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(y) |
+                        reinterpret_cast<uintptr_t>(shared)) & 15u) == 0) {
+    for (int64_t i = threadIdx.x * N; i < dim; i += kRowThreads * N) {
+      float acc[N];
+#pragma unroll
+      for (int k = 0; k < N; ++k) acc[k] = 0.f;
+      for (int j = 0; j < top_k; ++j) {
+        const float w = topk_w != nullptr ? topk_w[t * top_k + j] : 1.f;
+        const Vec16<T> v = ldv(y + (int64_t)inv_pos[t * top_k + j] * dim + i);
+#pragma unroll
+        for (int k = 0; k < N; ++k) acc[k] += w * to_f32<T>(v.e()[k]);
+      }
+      if (shared != nullptr) {
+        const Vec16<T> v = ldv(shared + t * dim + i);
+#pragma unroll
+        for (int k = 0; k < N; ++k) acc[k] += sg * to_f32<T>(v.e()[k]);
+      }
+      Vec16<T> o;
+#pragma unroll
+      for (int k = 0; k < N; ++k) o.e()[k] = from_f32<T>(acc[k]);
+      stv(out + t * dim + i, o);
+    }
+    return;
+  }
   for (int64_t i = threadIdx.x; i < dim; i += kRowThreads) {
     float acc = 0.f;
     for (int j = 0; j < top_k; ++j) {
@@ -324,11 +402,19 @@ int spd_act_and_mul(void* out, const void* x, int64_t rows, int64_t inter, int a
   SPD_REQUIRE(out && x, SPD_E_BADARG, "spd_act_and_mul: null pointer");
   SPD_REQUIRE(rows >= 0 && inter > 0 && (act == 0 || act == 1), SPD_E_BADARG, "spd_act_and_mul: bad arguments");
   if (rows == 0) return 0;
-  const int64_t n = rows * inter;
-  const unsigned grid = (unsigned)((n + kRowThreads - 1) / kRowThreads < 4096 ? (n + kRowThreads - 1) / kRowThreads : 4096);
   SPD_DISPATCH_ANY(dtype, {
-    SPD_CUDA(launch(act_and_mul_kernel<T>, dim3(grid), dim3(kRowThreads), 0, as_stream(stream), pdl_enabled(),
-                    (T*)out, (const T*)x, rows, inter, act));
+    constexpr int N = 16 / (int)sizeof(T);
+    const bool vec = inter % N == 0 && aligned16(out) && aligned16(x);
+    const int64_t n = vec ? rows * inter / N : rows * inter;
+    const int64_t blocks = (n + kRowThreads - 1) / kRowThreads;
+    const unsigned grid = (unsigned)(blocks < 8192 ? blocks : 8192);
+    if (vec) {
+      SPD_CUDA(launch(act_and_mul_vec_kernel<T>, dim3(grid), dim3(kRowThreads), 0, as_stream(stream), pdl_enabled(),
+                      (T*)out, (const T*)x, rows, inter, act));
+    } else {
+      SPD_CUDA(launch(act_and_mul_kernel<T>, dim3(grid), dim3(kRowThreads), 0, as_stream(stream), pdl_enabled(),
+                      (T*)out, (const T*)x, rows, inter, act));
+    }
   });
   return 0;
 }

@@ -691,10 +691,11 @@ def kv_store(key: torch.Tensor, value: torch.Tensor, k_pool: torch.Tensor, v_poo
 def attn_general(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, req_to_token, req_pool_indices,
                  num_q_heads: int, num_kv_heads: int, head_dim: int, v_dim: int, sm_scale: float, window: int = -1,
                  sinks: Optional[torch.Tensor] = None, slopes: Optional[torch.Tensor] = None, qtemp_coef: float = 0.0,
-                 qtemp_every: int = 0, seq_lens=None, prefix_lens=None, extend_lens=None, extend_start_loc=None
-                 ) -> torch.Tensor:
+                 qtemp_every: int = 0, seq_lens=None, prefix_lens=None, extend_lens=None, extend_start_loc=None,
+                 max_extend_len: int = 0) -> torch.Tensor:
     """Windowed / sink / distance-biased softmax attention over the paged pool; decode (seq_lens) or
-    ragged extend (prefix_lens, extend_lens, extend_start_loc).  q [T, H·head_dim] → [T, H·v_dim]."""
+    ragged extend (prefix_lens, extend_lens, extend_start_loc).  q [T, H·head_dim] → [T, H·v_dim].
+    max_extend_len > 0 (a host-side bound of extend_lens) lets 16-bit prefill run on the tensor cores."""
     _cuda(q, k_pool, v_pool, req_to_token, req_pool_indices, sinks, slopes)
     T = q.shape[0]
     if q.dim() != 2 or q.stride(1) != 1:
@@ -713,7 +714,7 @@ def attn_general(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, re
                                _ptr(extend_lens), _ptr(extend_start_loc), req_pool_indices.numel(), T, num_q_heads,
                                num_kv_heads, head_dim, v_dim, q.stride(0), out.stride(0), req_to_token.stride(0),
                                float(sm_scale), int(window), _ptr(sinks), _ptr(slopes), float(qtemp_coef),
-                               int(qtemp_every), _dta(q), _stream()), "spd_attn_general")
+                               int(qtemp_every), int(max_extend_len), _dta(q), _stream()), "spd_attn_general")
     return out
 
 
