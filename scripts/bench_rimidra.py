@@ -181,7 +181,8 @@ def kernel_table(z, flush):
     # prefill attention
     vis = sum(min(i + 1, win) for i in range(L)) * n_req
     ms = event_ms(lambda: ops.attn_general(q, kp, vp, r2t, rpi, H, G, D, D, D ** -0.5, win, sinks, slopes, 0.3, 128,
-                                           prefix_lens=pre, extend_lens=ext, extend_start_loc=start), flush=flush)
+                                           prefix_lens=pre, extend_lens=ext, extend_start_loc=start, max_extend_len=L),
+                  flush=flush)
     add(f"attn_general prefill {n_req}x{L} window {win}", "", ms, flops=4.0 * H * D * vis)
     full = sum(i + 1 for i in range(L)) * n_req
     ms = event_ms(lambda: ops.attn_prefill(q, kp, vp, r2t, rpi, pre, ext, start, L, H, G, D, D ** -0.5), flush=flush)

@@ -60,8 +60,6 @@ attn_general_kernel(T* __restrict__ out, const T* __restrict__ q, const T* __res
                     int dk, int dv, int64_t q_stride, int64_t out_stride, int64_t r2t_stride, float sm_scale,
                     int window, const float* __restrict__ sinks, const float* __restrict__ slopes, float qtemp_coef,
                     int qtemp_every) {
-  griddep_wait();
-  griddep_launch_dependents();
   extern __shared__ float q_smem[];  // [4][dk]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   // item = h * tokens_padded + t with tokens_padded a multiple of 4: the warps of a CTA share a head
@@ -152,8 +150,6 @@ attn_general_decode_kernel(T* __restrict__ out, const T* __restrict__ q, const T
                            int G, int dk, int dv, int64_t q_stride, int64_t out_stride, int64_t r2t_stride,
                            float sm_scale, int window, const float* __restrict__ sinks,
                            const float* __restrict__ slopes, float qtemp_coef, int qtemp_every) {
-  griddep_wait();
-  griddep_launch_dependents();
   extern __shared__ float dec_smem[];  // q [dk] | m [4] | l [4] | acc [4][dv]
   float* qs = dec_smem;
   float* sm_m = qs + dk;
@@ -239,8 +235,6 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 kv_store_kernel(const T* __restrict__ k, const T* __restrict__ v, T* __restrict__ k_pool, T* __restrict__ v_pool,
                 const int64_t* __restrict__ loc, int64_t k_row, int64_t v_row, int64_t k_stride, int64_t v_stride) {
-  griddep_wait();
-  griddep_launch_dependents();
   const int64_t t = blockIdx.x;
   const int64_t slot = loc[t];
   for (int64_t i = threadIdx.x; i < k_row; i += 256) k_pool[slot * k_row + i] = k[t * k_stride + i];
@@ -268,7 +262,7 @@ int spd_kv_store(const void* k, const void* v, void* k_pool, void* v_pool, const
   SPD_REQUIRE(tokens >= 0 && k_row_elems > 0 && v_row_elems >= 0, SPD_E_BADARG, "spd_kv_store: bad sizes");
   if (tokens == 0) return 0;
   SPD_DISPATCH_ANY(dtype, {
-    SPD_CUDA(launch(kv_store_kernel<T>, dim3((unsigned)tokens), dim3(256), 0, as_stream(stream), pdl_enabled(),
+    SPD_CUDA(launch(kv_store_kernel<T>, dim3((unsigned)tokens), dim3(256), 0, as_stream(stream), /*pdl=*/false,
                     (const T*)k, (const T*)v, (T*)k_pool, (T*)v_pool, loc, k_row_elems, v_row_elems, k_stride,
                     v_stride));
   });
@@ -297,7 +291,7 @@ int spd_attn_general(void* out, const void* q, const void* k_pool, const void* v
     const size_t dsmem = sizeof(float) * ((size_t)head_dim + 8 + 4 * (size_t)v_dim);
     SPD_DISPATCH_ANY(dtype, {
       SPD_CUDA(launch(attn_general_decode_kernel<T>, dim3((unsigned)batch, (unsigned)num_q_heads), dim3(128), dsmem,
-                      as_stream(stream), pdl_enabled(), (T*)out, (const T*)q, (const T*)k_pool, (const T*)v_pool,
+                      as_stream(stream), /*pdl=*/false, (T*)out, (const T*)q, (const T*)k_pool, (const T*)v_pool,
                       req_to_token, req_pool_indices, seq_lens, num_q_heads, num_kv_heads, head_dim, v_dim, q_stride,
                       out_stride, req_to_token_stride, sm_scale, window, sinks, slopes, qtemp_coef, qtemp_every));
     });
@@ -315,7 +309,7 @@ int spd_attn_general(void* out, const void* q, const void* k_pool, const void* v
   SPD_REQUIRE(ctas < (1ll << 31), SPD_E_SHAPE, "spd_attn_general: batch too large");
   const size_t smem = 4 * (size_t)head_dim * sizeof(float);
   SPD_DISPATCH_ANY(dtype, {
-    SPD_CUDA(launch(attn_general_kernel<T>, dim3((unsigned)ctas), dim3(128), smem, as_stream(stream), pdl_enabled(),
+    SPD_CUDA(launch(attn_general_kernel<T>, dim3((unsigned)ctas), dim3(128), smem, as_stream(stream), /*pdl=*/false,
                     (T*)out, (const T*)q, (const T*)k_pool, (const T*)v_pool, req_to_token, req_pool_indices, seq_lens,
                     prefix_lens, extend_lens, extend_start_loc, (int)batch, total_tokens, num_q_heads, num_kv_heads,
                     head_dim, v_dim, q_stride, out_stride, req_to_token_stride, sm_scale, window, sinks, slopes,

@@ -56,8 +56,6 @@ attn_general_mma_kernel(T* __restrict__ out, const T* __restrict__ q, const T* _
   T* sQ = reinterpret_cast<T*>(gm_smem);   // [BQ][LDK]
   T* sK = sQ + kGmBQ * LDK;                // [2][BK][LDK]
   T* sV = sK + 2 * kGmBK * LDK;            // [2][BK][LDV]
-  griddep_wait();
-  griddep_launch_dependents();
   const int r = blockIdx.y, h = blockIdx.z;
   const int ext = extend_lens[r];
   const int q0 = blockIdx.x * kGmBQ;
@@ -224,7 +222,7 @@ static int gm_launch(void* out, const void* q, const void* k_pool, const void* v
     configured = true;
   }
   const dim3 grid((unsigned)((max_extend_len + kGmBQ - 1) / kGmBQ), (unsigned)batch, (unsigned)H);
-  SPD_CUDA(launch(attn_general_mma_kernel<T, DK, DV>, grid, dim3(kGmThreads), smem, stream, pdl_enabled(), (T*)out,
+  SPD_CUDA(launch(attn_general_mma_kernel<T, DK, DV>, grid, dim3(kGmThreads), smem, stream, /*pdl=*/false, (T*)out,
                   (const T*)q, (const T*)k_pool, (const T*)v_pool, req_to_token, req_pool_indices, prefix_lens,
                   extend_lens, extend_start_loc, H, G, q_stride, out_stride, r2t_stride, sm_scale, window, sinks, slopes,
                   qtemp_coef, qtemp_every));
