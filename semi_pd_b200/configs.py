@@ -108,20 +108,28 @@ def _rimidra_config(path: str, cfg: dict, **overrides) -> ModelConfig:
     """config.json of the Rimidra family: {"architecture", "vocab", "width", "norm": {"eps"},
     "layers": [{"type", "mixer", "mlp", "weights_of"?}, ...]} — every size and constant of a layer is
     carried per layer in `layer_specs`; nothing is assumed equal across layers."""
-    layers = cfg["layers"]
+    layers = [dict(spec) for spec in cfg["layers"]]
     for i, spec in enumerate(layers):
         if spec["type"] not in ("attention", "retention"):
             raise ValueError(f"layer {i}: unknown mixer type {spec['type']!r}")
-        j = spec.get("weights_of")
-        if j is not None and (not 0 <= j < len(layers) or layers[j].get("weights_of") is not None
-                              or layers[j]["type"] != spec["type"]):
-            raise ValueError(f"layer {i}: weights_of {j} must name a layer of the same type with tensors of its own")
+        j, seen = spec.get("weights_of"), {i}
+        while j is not None:  # a borrowed layer may itself borrow: follow to the layer that owns tensors
+            if not 0 <= j < len(layers) or j in seen:
+                raise ValueError(f"layer {i}: weights_of {spec.get('weights_of')} does not lead to a layer with tensors")
+            seen.add(j)
+            if layers[j].get("weights_of") is None:
+                break
+            j = layers[j]["weights_of"]
+        if j is not None:
+            if layers[j]["type"] != spec["type"]:
+                raise ValueError(f"layer {i}: weights_of {j} names a layer of another mixer type")
+            spec["weights_of"] = int(j)
     attn = [s["mixer"] for s in layers if s["type"] == "attention"]
     kw = dict(model_type="rimidra", hidden_size=int(cfg["width"]), vocab_size=int(cfg["vocab"]),
               num_hidden_layers=len(layers), rms_norm_eps=float(cfg["norm"]["eps"]), layer_specs=layers,
               # summary fields other components print or size by; the per-layer values rule
               num_attention_heads=max([m["heads"] for m in attn] or [1]),
-              num_key_value_heads=max([m["kv_heads"] for m in attn] or [1]),
+              num_key_value_heads=max([m.get("kv_heads", m["heads"]) for m in attn] or [1]),
               head_dim=max([m["dim"] for m in attn] or [1]), intermediate_size=0,
               max_position_embeddings=int(cfg.get("context", 8192)))
     kw.update(overrides)
