@@ -151,6 +151,10 @@ def _paged(seq_k, seq_v, dtype, extra_slots=37, seed=0):
     dict(H=1, G=1, dk=8, dv=8, window=1, sink=True, slopes=False, qt=None),
     dict(H=8, G=2, dk=64, dv=64, window=130, sink=True, slopes=True, qt=(0.3, 128)),
     dict(H=3, G=3, dk=24, dv=40, window=-1, sink=False, slopes=True, qt=(0.2, 5)),
+    # shapes of the grouped decode kernel: 3, 8 and 1 query heads per key/value head, every value width
+    dict(H=6, G=2, dk=32, dv=128, window=33, sink=True, slopes=True, qt=(0.3, 7)),
+    dict(H=16, G=2, dk=16, dv=32, window=200, sink=True, slopes=True, qt=None),
+    dict(H=2, G=2, dk=128, dv=256, window=-1, sink=True, slopes=True, qt=(0.1, 64)),
 ])
 def test_attention_kernel_prefill_chunks_and_decode(dtype, case):
     """One sequence of 300 tokens over scattered slots: a portion with a prefix, a portion from the
@@ -186,6 +190,41 @@ def test_attention_kernel_prefill_chunks_and_decode(dtype, case):
         got = ops.attn_general(qd[pos:pos + 1].contiguous(), kp, vp, r2t, rpi,
                                seq_lens=torch.tensor([pos + 1], dtype=torch.int64, device=DEV), **kw)
         _close(got, want[pos:pos + 1], dt, f"decode at {pos}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("shape", [dict(H=8, G=2, dk=64, dv=64), dict(H=4, G=4, dk=32, dv=32), dict(H=5, G=1, dk=16, dv=24)])
+def test_attention_decode_batch_of_unequal_requests(dtype, shape):
+    """Five requests of unequal length decode in one launch (slots interleaved in one pool, request
+    rows out of order): every row equals the whole-sequence oracle of its own request."""
+    from semi_pd_b200 import ops
+    dt = DT[dtype]
+    Hh, G, dk, dv = shape["H"], shape["G"], shape["dk"], shape["dv"]
+    window, lens = 70, [1, 69, 70, 71, 260]
+    g = torch.Generator().manual_seed(11)
+    total = sum(lens)
+    perm = torch.randperm(total + 50, generator=g)[:total] + 1
+    kp = torch.randn(total + 51, G, dk, generator=g).to(dt)
+    vp = torch.randn(total + 51, G, dv, generator=g).to(dt)
+    r2t = torch.zeros(8, 320, dtype=torch.int32)
+    sinks, slopes = torch.randn(Hh, generator=g), R.distance_slopes(Hh)
+    rows, qs, wants, at = [7, 2, 5, 0, 3], [], [], 0
+    for n, row in zip(lens, rows):
+        q = torch.randn(n, Hh, dk, generator=g).to(dt)
+        k = torch.randn(n, G, dk, generator=g).to(dt)
+        v = torch.randn(n, G, dv, generator=g).to(dt)
+        sl = perm[at:at + n]
+        at += n
+        kp[sl], vp[sl] = k, v
+        r2t[row, :n] = sl.int()
+        wants.append(R.windowed_sink_attention(q.double(), k.double(), v.double(), 0.25, window, sinks, slopes,
+                                               (0.3, 32)).reshape(n, Hh * dv)[-1])
+        qs.append(q[-1].reshape(Hh * dk))
+    got = ops.attn_general(torch.stack(qs).to(DEV), kp.to(DEV), vp.to(DEV), r2t.to(DEV),
+                           torch.tensor(rows, dtype=torch.int64, device=DEV), num_q_heads=Hh, num_kv_heads=G, head_dim=dk,
+                           v_dim=dv, sm_scale=0.25, window=window, sinks=sinks.to(DEV), slopes=slopes.float().to(DEV),
+                           qtemp_coef=0.3, qtemp_every=32, seq_lens=torch.tensor(lens, dtype=torch.int64, device=DEV))
+    _close(got, torch.stack(wants), dt, "batched decode")
 
 
 @pytest.mark.parametrize("mode", ["extend", "decode"])
