@@ -265,11 +265,11 @@ def run(sizes=("s", "m"), out=None, kernels=True):
         for label, cfg in (("llama", llama_config(z)), ("rimidra-dense", rimidra_config(z, False)),
                            ("rimidra-moe", rimidra_config(z, True))):
             entry["models"][label] = model_throughput(cfg, n_prompts=4, prompt_len=2048, decode_bs=64, flush=flush)
-            print(name, label, json.dumps(entry["models"][label]), flush=True)
+            print(name, label, json.dumps(entry["models"][label]), file=sys.stderr, flush=True)
         if kernels:
             entry["kernels"] = kernel_table(z, flush)
             for r in entry["kernels"]:
-                print(name, json.dumps(r), flush=True)
+                print(name, json.dumps(r), file=sys.stderr, flush=True)
         res["sizes"][name] = entry
     if out:
         with open(out, "w") as f:
