@@ -13,6 +13,7 @@ from __future__ import annotations
 
 import bisect
 import dataclasses
+import gc
 import logging
 import os
 from typing import Optional
@@ -270,10 +271,20 @@ class CudaGraphRunner:
     def capture(self):
         set_current_comm(self.model_runner.tp_comm)
         stream = torch.cuda.current_stream()
-        for bs in reversed(self.capture_bs):
-            graph, out = self.capture_one_batch_size(bs, stream)
-            self.graphs[bs] = graph
-            self.output_buffers[bs] = out
+        # No garbage collection while a stream is capturing: a collector run that frees an older
+        # runner's graphs or device memory in the middle of a capture is an operation the capture
+        # does not permit, and invalidates it (seen when a second engine was built in one process).
+        gc.collect()
+        gc_was_enabled = gc.isenabled()
+        gc.disable()
+        try:
+            for bs in reversed(self.capture_bs):
+                graph, out = self.capture_one_batch_size(bs, stream)
+                self.graphs[bs] = graph
+                self.output_buffers[bs] = out
+        finally:
+            if gc_was_enabled:
+                gc.enable()
 
     def capture_one_batch_size(self, bs: int, stream):
         mr = self.model_runner
