@@ -621,12 +621,31 @@ def linear_any(x: torch.Tensor, weight: torch.Tensor, out_f32: bool = False) -> 
 
 
 def linear_grouped_any(x_sorted: torch.Tensor, weight: torch.Tensor, tile_group: torch.Tensor, num_groups: int,
-                       n: int) -> torch.Tensor:
-    """Expert-grouped F.linear over 128-row tiles; weight = the experts' [n, K] matrices stacked."""
+                       n: int, silu_mul: bool = False) -> torch.Tensor:
+    """Expert-grouped F.linear over 128-row tiles; weight = the experts' [n, K] matrices stacked.
+    silu_mul: each expert's block is [gate; up] (2n rows) and the result is silu(gate) * up [rows, n] —
+    the tensor-core GEMM applies it to its fp32 accumulators in the epilogue, the CUDA-core route runs
+    the activation kernel on the product."""
     if (_tc_gemm_ok(x_sorted, weight, n) and x_sorted.shape[1] % 64 == 0
             and os.environ.get("SPD_HYBRID_GEMM", "tc") == "tc"):
-        return linear_grouped_rows(x_sorted, weight, tile_group, num_groups, n)
-    return linear_simt(x_sorted, weight, tile_group=tile_group, group_rows=n, n=n)
+        if silu_mul and os.environ.get("SPD_HYBRID_FUSED_ACT", "1") != "1":
+            return act_and_mul(linear_grouped_rows(x_sorted, weight, tile_group, num_groups, 2 * n), "silu")
+        return linear_grouped_rows(x_sorted, weight, tile_group, num_groups, n,
+                                   epilogue=SPD_EPI_SILU_MUL if silu_mul else SPD_EPI_NONE)
+    rows = 2 * n if silu_mul else n
+    y = linear_simt(x_sorted, weight, tile_group=tile_group, group_rows=rows, n=rows)
+    return act_and_mul(y, "silu") if silu_mul else y
+
+
+def linear_silu_mul_any(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """silu(x W_gate^T) * (x W_up^T) for weight = [W_gate; W_up]: one tensor-core GEMM with the
+    activation in its epilogue for prefill-sized 16-bit batches (the Llama MLP's route), GEMM +
+    activation kernel otherwise."""
+    n = weight.shape[0] // 2
+    if (x.shape[0] >= 257 and _tc_gemm_ok(x, weight, n) and os.environ.get("SPD_HYBRID_GEMM", "tc") == "tc"
+            and os.environ.get("SPD_HYBRID_FUSED_ACT", "1") == "1"):
+        return linear(x, weight, epilogue=SPD_EPI_SILU_MUL)
+    return act_and_mul(linear_any(x, weight), "silu")
 
 
 def moe_route_scores(logits: torch.Tensor, num_experts: int, top_k: int, score_func: str = "sigmoid",

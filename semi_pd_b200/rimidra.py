@@ -139,6 +139,8 @@ class RimidraDenseMLP:
         self.gate_up_proj, self.down_proj = _W(), _W()
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
+        if self.act == "silu":
+            return ops.linear_any(ops.linear_silu_mul_any(h, self.gate_up_proj.weight), self.down_proj.weight)
         gate_up = ops.linear_any(h, self.gate_up_proj.weight)
         return ops.linear_any(ops.act_and_mul(gate_up, self.act), self.down_proj.weight)
 
@@ -165,7 +167,7 @@ class RimidraMoE:
         ids, w = ops.moe_route_scores(z, E, self.top_k, score_func="sigmoid", renormalize=False)
         row_token, inv_pos, tile_group = ops.moe_align(ids, E)
         xs = ops.moe_gather_scaled(h, row_token, inv_pos, w)
-        act = ops.act_and_mul(ops.linear_grouped_any(xs, self.w_gate_up.weight, tile_group, E, 2 * self.ff), "silu")
+        act = ops.linear_grouped_any(xs, self.w_gate_up.weight, tile_group, E, self.ff, silu_mul=True)
         y = ops.linear_grouped_any(act, self.w_down.weight, tile_group, E, self.hidden)
         shared = self.shared(h) if self.shared is not None else None
         return ops.moe_combine_gated(y, inv_pos, T, self.top_k, topk_w=None, shared=shared,

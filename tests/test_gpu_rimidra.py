@@ -134,6 +134,28 @@ def test_moe_pieces(dtype, experts, top):
     _close(got, want, dt, "moe output")
 
 
+@pytest.mark.parametrize("ff", [24, 96, 128, 200, 704])
+def test_silu_mul_in_the_gemm_epilogue(ff):
+    """silu(gate) * up applied by the tensor-core GEMMs to their accumulators — grouped (experts) and
+    plain (a shared expert at prefill size) — against float64, for widths on and off the 128-row tile."""
+    from semi_pd_b200 import ops
+    dt, Wd, E, T = torch.bfloat16, 128, 3, 300
+    g = torch.Generator().manual_seed(ff)
+    x = torch.randn(T, Wd, generator=g).to(dt)
+    wgu = (torch.randn(E * 2 * ff, Wd, generator=g) / Wd ** 0.5).to(dt)
+    ids = torch.randint(0, E, (T, 1), generator=g).int()
+    row_token, inv_pos, tile_group = ops.moe_align(ids.to(DEV), E)
+    xs = ops.moe_gather_scaled(x.to(DEV), row_token, inv_pos, None)
+    got = ops.linear_grouped_any(xs, wgu.to(DEV), tile_group, E, ff, silu_mul=True)
+    pos = inv_pos.cpu().long().reshape(T)
+    for t in range(0, T, 7):
+        e = int(ids[t, 0])
+        gu = wgu.double()[e * 2 * ff:(e + 1) * 2 * ff] @ x[t].double()
+        _close(got[pos[t]], R.silu(gu[:ff]) * gu[ff:], dt, f"expert row {t}")
+    gu = x.double() @ wgu.double()[:2 * ff].T
+    _close(ops.linear_silu_mul_any(x.to(DEV), wgu[:2 * ff].to(DEV)), R.silu(gu[:, :ff]) * gu[:, ff:], dt, "plain")
+
+
 def _paged(seq_k, seq_v, dtype, extra_slots=37, seed=0):
     """Scatter a sequence's K / V rows over a pool in a random slot order; → pools, page table row."""
     T = seq_k.shape[0]
