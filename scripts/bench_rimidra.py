@@ -17,6 +17,7 @@ SIZES = {
     # name: width, layers, heads, kv_heads, head_dim, ff, window, experts, top, expert ff
     "s": dict(width=1024, layers=8, heads=8, kv_heads=2, dim=128, ff=2816, window=512, experts=8, top=2, eff=704),
     "m": dict(width=2048, layers=8, heads=16, kv_heads=4, dim=128, ff=5632, window=1024, experts=16, top=2, eff=1408),
+    "l": dict(width=4096, layers=8, heads=32, kv_heads=8, dim=128, ff=11008, window=2048, experts=16, top=2, eff=2816),
 }
 VOCAB = 32000
 FP32_CORE_TFLOPS = 148 * 128 * 2 * 1.965e9 / 1e12  # FMA units x 2 flop x max clock: the CUDA-core ceiling
