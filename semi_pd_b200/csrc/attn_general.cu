@@ -466,6 +466,12 @@ int attn_general_mma_try(void* out, const void* q, const void* k_pool, const voi
                          const float* sinks, const float* slopes, float qtemp_coef, int qtemp_every, int dtype,
                          cudaStream_t stream);
 
+int attn_general_mma_decode_try(void* out, const void* q, const void* k_pool, const void* v_pool,
+                                const int32_t* req_to_token, const int64_t* req_pool_indices, const int64_t* seq_lens,
+                                int64_t batch, int H, int G, int dk, int dv, int64_t q_stride, int64_t out_stride,
+                                int64_t r2t_stride, float sm_scale, int window, const float* sinks, const float* slopes,
+                                float qtemp_coef, int qtemp_every, int dtype, cudaStream_t stream);
+
 }  // namespace spd
 
 using namespace spd;
@@ -505,6 +511,14 @@ int spd_attn_general(void* out, const void* q, const void* k_pool, const void* v
   if (total_tokens == 0 || batch == 0) return 0;
   if (seq_lens != nullptr) {
     SPD_REQUIRE(batch < (1ll << 31) && num_q_heads <= 65535, SPD_E_SHAPE, "spd_attn_general: batch too large");
+    // 16-bit models, instantiated head sizes: the tensor-core form (SPD_ATTN_DECODE_SIMT=1 keeps the CUDA cores)
+    if (getenv("SPD_ATTN_DECODE_SIMT") == nullptr) {
+      const int rc = attn_general_mma_decode_try(out, q, k_pool, v_pool, req_to_token, req_pool_indices, seq_lens, batch,
+                                                 num_q_heads, num_kv_heads, head_dim, v_dim, q_stride, out_stride,
+                                                 req_to_token_stride, sm_scale, window, sinks, slopes, qtemp_coef,
+                                                 qtemp_every, dtype, as_stream(stream));
+      if (rc != 1) return rc;
+    }
     // grouped form: 16-byte rows, v_dim 32 x {1, 2, 4, 8}, up to 8 query heads per key/value head
     const int R = num_q_heads / num_kv_heads;
     const size_t esz = dtype == SPD_F32 ? 4 : 2;

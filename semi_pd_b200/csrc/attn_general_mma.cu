@@ -262,4 +262,254 @@ int attn_general_mma_try(void* out, const void* q, const void* k_pool, const voi
   return 1;
 }
 
+// ------------------------------------------------------------------------------------------------
+// Decode on the tensor cores: one CTA per (request, key/value head); the R = H / G query heads that
+// share the head are the 16 rows of the MMA's A operand (rows >= R are zero), so a K / V row leaves
+// the pool once per group and a tile of 32 keys costs 2 * DK / 16 + DV / 4 MMAs instead of 64 R FMAs
+// per lane.  The NW warps take the window's key tiles in turn (tile i goes to warp i mod NW); a warp
+// stages its own tile with 16-byte cp.async (rows past the end are zero-filled) and keeps the
+// online-softmax state of the 16 rows in the accumulator layout; at the end the warps' partial
+// (max, sum, output) triples meet in shared memory, where the sink enters the denominator once.
+// Everything but the two products' operands (q, k, v, and P rounded to 16 bits) is fp32.
+// ------------------------------------------------------------------------------------------------
+constexpr int kGdTK = 32;        // keys per warp tile
+constexpr int kGdWarpHdr = 128;  // bytes in front of a warp's tiles: its slot numbers
+
+template <typename T, int DK, int DV, int NW>
+__global__ void __launch_bounds__(NW * 32)
+attn_general_mma_decode_kernel(T* __restrict__ out, const T* __restrict__ q, const T* __restrict__ k_pool,
+                               const T* __restrict__ v_pool, const int32_t* __restrict__ req_to_token,
+                               const int64_t* __restrict__ req_pool_indices, const int64_t* __restrict__ seq_lens,
+                               int H, int G, int64_t q_stride, int64_t out_stride, int64_t r2t_stride, float sm_scale,
+                               int window, const float* __restrict__ sinks, const float* __restrict__ slopes,
+                               float qtemp_coef, int qtemp_every) {
+  constexpr int LDK = DK + 8, LDV = DV + 8;
+  constexpr size_t kQBytes = sizeof(T) * 16 * LDK;
+  constexpr size_t kWarpBytes = kGdWarpHdr + sizeof(T) * kGdTK * (LDK + LDV);
+  extern __shared__ __align__(16) unsigned char gd_smem[];
+  T* sQ = reinterpret_cast<T*>(gd_smem);  // [16][LDK], rows >= R zero
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int r = blockIdx.x, g = blockIdx.y;
+  const int R = H / G;
+  const int64_t pos = seq_lens[r] - 1;
+  if (pos < 0) return;
+  unsigned char* wbase = gd_smem + kQBytes + (size_t)warp * kWarpBytes;
+  int* slots = reinterpret_cast<int*>(wbase);
+  T* sK = reinterpret_cast<T*>(wbase + kGdWarpHdr);  // [32][LDK]
+  T* sV = sK + kGdTK * LDK;                          // [32][LDV]
+  const int32_t* page = req_to_token + req_pool_indices[r] * r2t_stride;
+  for (int idx = tid; idx < 16 * (DK / 8); idx += NW * 32) {
+    const int row = idx / (DK / 8), c = idx % (DK / 8);
+    const bool ok = row < R;
+    cp_async16(smem_u32(sQ + row * LDK + c * 8), q + (int64_t)r * q_stride + ((int64_t)g * R + (ok ? row : 0)) * DK + c * 8, ok);
+  }
+  cp_async_commit();
+  cp_async_wait<0>();
+  __syncthreads();
+
+  const int rr[2] = {lane >> 2, (lane >> 2) + 8};  // this thread's two rows (query heads of the group)
+  float temp = 1.f;
+  if (qtemp_every > 0) temp = 1.f + qtemp_coef * logf((float)((pos + 1) / qtemp_every + 1));
+  const float sc = sm_scale * temp * kLog2e;
+  float sl[2];
+#pragma unroll
+  for (int x = 0; x < 2; ++x) sl[x] = (slopes != nullptr && rr[x] < R) ? slopes[g * R + rr[x]] * kLog2e : 0.f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};  // l: this thread's share of the row sum
+  float o[DV / 8][4];
+#pragma unroll
+  for (int i = 0; i < DV / 8; ++i)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[i][e] = 0.f;
+
+  constexpr int kc = DK / 8, vc = DV / 8;  // 16-byte chunks per row; both divide 32
+  const int64_t j_lo = window > 0 ? (pos - window + 1 > 0 ? pos - window + 1 : 0) : 0;
+  for (int64_t j0 = j_lo + kGdTK * warp; j0 <= pos; j0 += kGdTK * NW) {
+    const int n = (int)(pos - j0 + 1 < kGdTK ? pos - j0 + 1 : kGdTK);
+    __syncwarp();  // the previous tile has been read
+    if (lane < n) slots[lane] = page[j0 + lane];
+    __syncwarp();
+    for (int row = lane / kc; row < kGdTK; row += 32 / kc) {
+      const bool ok = row < n;
+      const int64_t slot = ok ? slots[row] : 0;
+      cp_async16(smem_u32(sK + row * LDK + (lane % kc) * 8), k_pool + (slot * G + g) * DK + (lane % kc) * 8, ok);
+    }
+    for (int row = lane / vc; row < kGdTK; row += 32 / vc) {
+      const bool ok = row < n;
+      const int64_t slot = ok ? slots[row] : 0;
+      cp_async16(smem_u32(sV + row * LDV + (lane % vc) * 8), v_pool + (slot * G + g) * DV + (lane % vc) * 8, ok);
+    }
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncwarp();
+
+    float s[kGdTK / 8][4];
+#pragma unroll
+    for (int i = 0; i < kGdTK / 8; ++i)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s[i][e] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < DK / 16; ++kk) {
+      uint32_t a[4];
+      gm_ldsm_x4(a, sQ + ((lane & 7) + ((lane >> 3) & 1) * 8) * LDK + kk * 16 + (lane >> 4) * 8);
+#pragma unroll
+      for (int nb2 = 0; nb2 < kGdTK / 16; ++nb2) {
+        uint32_t b[4];
+        gm_ldsm_x4(b, sK + (nb2 * 16 + (lane & 7) + (lane >> 4) * 8) * LDK + kk * 16 + ((lane >> 3) & 1) * 8);
+        gm_mma<T>(s[2 * nb2], a, b[0], b[1]);
+        gm_mma<T>(s[2 * nb2 + 1], a, b[2], b[3]);
+      }
+    }
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nb = 0; nb < kGdTK / 8; ++nb)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int x = e >> 1;
+        const int col = nb * 8 + (lane & 3) * 2 + (e & 1);
+        const float v = col < n ? s[nb][e] * sc - sl[x] * (float)(pos - (j0 + col)) : -INFINITY;
+        s[nb][e] = v;
+        mx[x] = fmaxf(mx[x], v);
+      }
+    float ms[2];
+#pragma unroll
+    for (int x = 0; x < 2; ++x) {
+      mx[x] = fmaxf(mx[x], __shfl_xor_sync(0xffffffffu, mx[x], 1));
+      mx[x] = fmaxf(mx[x], __shfl_xor_sync(0xffffffffu, mx[x], 2));
+      const float m_new = fmaxf(m[x], mx[x]);
+      ms[x] = m_new == -INFINITY ? 0.f : m_new;
+      const float corr = exp2f(m[x] - ms[x]);  // m = -inf: 0 (nothing accumulated yet)
+      m[x] = m_new;
+      l[x] *= corr;
+#pragma unroll
+      for (int i = 0; i < DV / 8; ++i) {
+        o[i][2 * x] *= corr;
+        o[i][2 * x + 1] *= corr;
+      }
+    }
+#pragma unroll
+    for (int nb = 0; nb < kGdTK / 8; ++nb)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float p = exp2f(s[nb][e] - ms[e >> 1]);
+        s[nb][e] = p;
+        l[e >> 1] += p;
+      }
+#pragma unroll
+    for (int kk = 0; kk < kGdTK / 16; ++kk) {
+      uint32_t a[4];
+      a[0] = pack2<T>(s[2 * kk][0], s[2 * kk][1]);
+      a[1] = pack2<T>(s[2 * kk][2], s[2 * kk][3]);
+      a[2] = pack2<T>(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+      a[3] = pack2<T>(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+      for (int nb2 = 0; nb2 < DV / 16; ++nb2) {
+        uint32_t b[4];
+        gm_ldsm_x4_trans(b, sV + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDV + nb2 * 16 + (lane >> 4) * 8);
+        gm_mma<T>(o[2 * nb2], a, b[0], b[1]);
+        gm_mma<T>(o[2 * nb2 + 1], a, b[2], b[3]);
+      }
+    }
+  }
+#pragma unroll
+  for (int x = 0; x < 2; ++x) {
+    l[x] += __shfl_xor_sync(0xffffffffu, l[x], 1);
+    l[x] += __shfl_xor_sync(0xffffffffu, l[x], 2);
+  }
+  __syncthreads();  // the tiles are dead: their shared memory carries the partials
+  float* pm = reinterpret_cast<float*>(gd_smem + kQBytes);  // [NW][16]
+  float* pl = pm + NW * 16;                                 // [NW][16]
+  float* po = pl + NW * 16;                                 // [NW][16][DV]
+#pragma unroll
+  for (int x = 0; x < 2; ++x) {
+    if ((lane & 3) == 0) {
+      pm[warp * 16 + rr[x]] = m[x];
+      pl[warp * 16 + rr[x]] = l[x];
+    }
+#pragma unroll
+    for (int nb = 0; nb < DV / 8; ++nb) {
+      float* dst = po + (size_t)(warp * 16 + rr[x]) * DV + nb * 8 + (lane & 3) * 2;
+      dst[0] = o[nb][2 * x];
+      dst[1] = o[nb][2 * x + 1];
+    }
+  }
+  __syncthreads();
+  for (int idx = tid; idx < R * DV; idx += NW * 32) {
+    const int row = idx / DV, c = idx - row * DV;
+    const int h = g * R + row;
+    const float sink2 = sinks != nullptr ? sinks[h] * kLog2e : -INFINITY;
+    float mt = sink2;
+#pragma unroll
+    for (int w = 0; w < NW; ++w) mt = fmaxf(mt, pm[w * 16 + row]);
+    float lt = sinks != nullptr ? exp2f(sink2 - mt) : 0.f;
+    float acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < NW; ++w) {
+      const float mw = pm[w * 16 + row];
+      const float f = mw == -INFINITY ? 0.f : exp2f(mw - mt);  // a warp without keys adds nothing
+      lt += pl[w * 16 + row] * f;
+      acc += po[(size_t)(w * 16 + row) * DV + c] * f;
+    }
+    out[(int64_t)r * out_stride + (int64_t)h * DV + c] = from_f32<T>(acc / lt);
+  }
+}
+
+template <typename T, int DK, int DV, int NW>
+static int gd_launch_nw(void* out, const void* q, const void* k_pool, const void* v_pool, const int32_t* req_to_token,
+                        const int64_t* req_pool_indices, const int64_t* seq_lens, int64_t batch, int H, int G,
+                        int64_t q_stride, int64_t out_stride, int64_t r2t_stride, float sm_scale, int window,
+                        const float* sinks, const float* slopes, float qtemp_coef, int qtemp_every, cudaStream_t stream) {
+  constexpr size_t tiles = (size_t)NW * (kGdWarpHdr + sizeof(T) * kGdTK * (DK + 8 + DV + 8));
+  constexpr size_t merge = sizeof(float) * NW * 16 * (DV + 2);
+  constexpr size_t smem = sizeof(T) * 16 * (DK + 8) + (tiles > merge ? tiles : merge);
+  static bool configured = false;  // per instantiation
+  if (!configured) {
+    SPD_CUDA(cudaFuncSetAttribute(attn_general_mma_decode_kernel<T, DK, DV, NW>,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = true;
+  }
+  SPD_CUDA(launch(attn_general_mma_decode_kernel<T, DK, DV, NW>, dim3((unsigned)batch, (unsigned)G), dim3(NW * 32), smem,
+                  stream, /*pdl=*/false, (T*)out, (const T*)q, (const T*)k_pool, (const T*)v_pool, req_to_token,
+                  req_pool_indices, seq_lens, H, G, q_stride, out_stride, r2t_stride, sm_scale, window, sinks, slopes,
+                  qtemp_coef, qtemp_every));
+  return 0;
+}
+
+// → 0 launched, 1 not applicable (the caller falls back to the CUDA-core decode kernels), else an error
+int attn_general_mma_decode_try(void* out, const void* q, const void* k_pool, const void* v_pool,
+                                const int32_t* req_to_token, const int64_t* req_pool_indices, const int64_t* seq_lens,
+                                int64_t batch, int H, int G, int dk, int dv, int64_t q_stride, int64_t out_stride,
+                                int64_t r2t_stride, float sm_scale, int window, const float* sinks, const float* slopes,
+                                float qtemp_coef, int qtemp_every, int dtype, cudaStream_t stream) {
+  if (dtype != SPD_BF16 && dtype != SPD_F16) return 1;
+  if (H / G > 16 || G > 65535 || batch >= (1ll << 31)) return 1;
+  if (q_stride % 8 != 0 || !aligned16(q) || !aligned16(k_pool) || !aligned16(v_pool)) return 1;
+  // short windows do not fill eight warps: four warps then leave room for more CTAs per SM
+  const bool wide = window <= 0 || window > 4 * kGdTK;
+#define SPD_GD_CASE(DKV, DVV)                                                                                         \
+  if (dk == DKV && dv == DVV) {                                                                                       \
+    if (dtype == SPD_BF16)                                                                                            \
+      return wide ? gd_launch_nw<__nv_bfloat16, DKV, DVV, 8>(out, q, k_pool, v_pool, req_to_token, req_pool_indices,  \
+                                                             seq_lens, batch, H, G, q_stride, out_stride, r2t_stride, \
+                                                             sm_scale, window, sinks, slopes, qtemp_coef, qtemp_every, \
+                                                             stream)                                                  \
+                  : gd_launch_nw<__nv_bfloat16, DKV, DVV, 4>(out, q, k_pool, v_pool, req_to_token, req_pool_indices,  \
+                                                             seq_lens, batch, H, G, q_stride, out_stride, r2t_stride, \
+                                                             sm_scale, window, sinks, slopes, qtemp_coef, qtemp_every, \
+                                                             stream);                                                 \
+    return wide ? gd_launch_nw<__half, DKV, DVV, 8>(out, q, k_pool, v_pool, req_to_token, req_pool_indices, seq_lens, \
+                                                    batch, H, G, q_stride, out_stride, r2t_stride, sm_scale, window,  \
+                                                    sinks, slopes, qtemp_coef, qtemp_every, stream)                   \
+                : gd_launch_nw<__half, DKV, DVV, 4>(out, q, k_pool, v_pool, req_to_token, req_pool_indices, seq_lens, \
+                                                    batch, H, G, q_stride, out_stride, r2t_stride, sm_scale, window,  \
+                                                    sinks, slopes, qtemp_coef, qtemp_every, stream);                  \
+  }
+  SPD_GD_CASE(32, 32)
+  SPD_GD_CASE(64, 64)
+  SPD_GD_CASE(64, 128)
+  SPD_GD_CASE(128, 64)
+  SPD_GD_CASE(128, 128)
+#undef SPD_GD_CASE
+  return 1;
+}
+
 }  // namespace spd

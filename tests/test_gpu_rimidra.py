@@ -177,6 +177,10 @@ def _paged(seq_k, seq_v, dtype, extra_slots=37, seed=0):
     dict(H=6, G=2, dk=32, dv=128, window=33, sink=True, slopes=True, qt=(0.3, 7)),
     dict(H=16, G=2, dk=16, dv=32, window=200, sink=True, slopes=True, qt=None),
     dict(H=2, G=2, dk=128, dv=256, window=-1, sink=True, slopes=True, qt=(0.1, 64)),
+    # head sizes of the tensor-core kernels: 4, 12 and 1 query heads per key/value head
+    dict(H=8, G=2, dk=128, dv=128, window=100, sink=True, slopes=True, qt=(0.3, 128)),
+    dict(H=12, G=1, dk=64, dv=128, window=-1, sink=True, slopes=True, qt=(0.2, 9)),
+    dict(H=3, G=3, dk=128, dv=64, window=31, sink=False, slopes=True, qt=None),
 ])
 def test_attention_kernel_prefill_chunks_and_decode(dtype, case):
     """One sequence of 300 tokens over scattered slots: a portion with a prefix, a portion from the
@@ -215,7 +219,8 @@ def test_attention_kernel_prefill_chunks_and_decode(dtype, case):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("shape", [dict(H=8, G=2, dk=64, dv=64), dict(H=4, G=4, dk=32, dv=32), dict(H=5, G=1, dk=16, dv=24)])
+@pytest.mark.parametrize("shape", [dict(H=8, G=2, dk=64, dv=64), dict(H=4, G=4, dk=32, dv=32), dict(H=5, G=1, dk=16, dv=24),
+                                   dict(H=16, G=1, dk=128, dv=128), dict(H=6, G=3, dk=64, dv=128)])
 def test_attention_decode_batch_of_unequal_requests(dtype, shape):
     """Five requests of unequal length decode in one launch (slots interleaved in one pool, request
     rows out of order): every row equals the whole-sequence oracle of its own request."""
