@@ -7,7 +7,8 @@
 // of the state in registers: warp w holds the ROWS consecutive state rows w * ROWS .. and lane l
 // the column l, so a token costs a thread two 16-byte shared-memory loads per four rows and
 // 3 * ROWS FMAs, and W = head_dim / ROWS warps (4 to 16) share a token.  The request's new tokens
-// are walked in blocks of 16 staged through shared memory (rows zero-padded to W * ROWS); the
+// are walked in blocks of 16 (decode: its one token) staged through shared memory (rows zero-padded
+// to W * ROWS); the
 // warps' partial outputs of a block meet in shared memory once per block; the state goes back to
 // the request's slot at the end.  Every output element is summed in one fixed order (rows of a
 // thread ascending over two interleaved accumulators, then warps ascending), so o does not depend
@@ -25,10 +26,10 @@
 
 namespace spd {
 
-constexpr int kRetTok = 16;   // tokens staged per block
+constexpr int kRetTok = 16;   // tokens staged per block (extend); decode stages its one token
 constexpr int kRetCols = 32;  // value columns per CTA
 
-template <typename T, int W, int ROWS, bool ASYNC>  // W warps x ROWS state rows per thread >= head_dim
+template <typename T, int W, int ROWS, bool ASYNC, int TOK>  // W warps x ROWS state rows per thread >= head_dim; TOK tokens per block
 __global__ void __launch_bounds__(W * 32)
 retention_kernel(float* __restrict__ o, const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
                  float* __restrict__ state, const int64_t* __restrict__ req_pool_indices,
@@ -42,14 +43,14 @@ retention_kernel(float* __restrict__ o, const T* __restrict__ q, const T* __rest
   constexpr int NT = W * 32;
   constexpr int N = 16 / (int)sizeof(T);
   extern __shared__ __align__(16) float smem[];
-  float* qs = smem;                       // [kRetTok][DKP] rotated
-  float* ks = qs + kRetTok * DKP;         // [kRetTok][DKP] rotated, scaled
-  float* vs = ks + kRetTok * DKP;         // [kRetTok][kRetCols]
-  float* part = vs + kRetTok * kRetCols;  // [W][kRetTok][kRetCols]
-  float* cs = part + W * kRetTok * kRetCols;               // ASYNC: [kRetTok][rot] raw cos || sin rows
-  T* rq = reinterpret_cast<T*>(cs + kRetTok * rot);        // ASYNC: [kRetTok][dk] raw
-  T* rk = rq + kRetTok * dk;                               // ASYNC: [kRetTok][dk] raw
-  T* rv = rk + kRetTok * dk;                               // ASYNC: [kRetTok][kRetCols] raw
+  float* qs = smem;                       // [TOK][DKP] rotated
+  float* ks = qs + TOK * DKP;         // [TOK][DKP] rotated, scaled
+  float* vs = ks + TOK * DKP;         // [TOK][kRetCols]
+  float* part = vs + TOK * kRetCols;  // [W][TOK][kRetCols]
+  float* cs = part + W * TOK * kRetCols;               // ASYNC: [TOK][rot] raw cos || sin rows
+  T* rq = reinterpret_cast<T*>(cs + TOK * rot);        // ASYNC: [TOK][dk] raw
+  T* rk = rq + TOK * dk;                               // ASYNC: [TOK][dk] raw
+  T* rv = rk + TOK * dk;                               // ASYNC: [TOK][kRetCols] raw
   const int r = blockIdx.x, h = blockIdx.y;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int col0 = blockIdx.z * kRetCols;
@@ -82,7 +83,7 @@ retention_kernel(float* __restrict__ o, const T* __restrict__ q, const T* __rest
   const int half = rot >> 1;
   const int qc = dk / N, vc = kRetCols / N, cc = rot / 4;  // ASYNC: 16-byte chunks per row
   auto fetch = [&](int t0) {
-    const int nt = n - t0 < kRetTok ? n - t0 : kRetTok;
+    const int nt = n - t0 < TOK ? n - t0 : TOK;
     for (int idx = threadIdx.x; idx < nt * qc; idx += NT) {
       const int tt = idx / qc, ch = idx - tt * qc;
       const int64_t row = row0 + t0 + tt;
@@ -104,8 +105,8 @@ retention_kernel(float* __restrict__ o, const T* __restrict__ q, const T* __rest
     cp_async_commit();
   };
   if (ASYNC) fetch(0);
-  for (int t0 = 0; t0 < n; t0 += kRetTok) {
-    const int nt = n - t0 < kRetTok ? n - t0 : kRetTok;
+  for (int t0 = 0; t0 < n; t0 += TOK) {
+    const int nt = n - t0 < TOK ? n - t0 : TOK;
     if (ASYNC) {
       cp_async_wait<0>();
       __syncthreads();  // raw rows of this block visible; the previous block's reduce has finished
@@ -164,7 +165,7 @@ retention_kernel(float* __restrict__ o, const T* __restrict__ q, const T* __rest
       }
     }
     __syncthreads();  // staging complete (ASYNC: the raw area is free again)
-    if (ASYNC && t0 + kRetTok < n) fetch(t0 + kRetTok);
+    if (ASYNC && t0 + TOK < n) fetch(t0 + TOK);
     for (int tt = 0; tt < nt; ++tt) {
       const float vv = vs[tt * kRetCols + lane];
       const float4* kt = reinterpret_cast<const float4*>(ks + tt * DKP + warp * ROWS);
@@ -182,13 +183,13 @@ retention_kernel(float* __restrict__ o, const T* __restrict__ q, const T* __rest
         S[4 * i + 3] = fmaf(dec, S[4 * i + 3], k4.w * vv);
         acc1 = fmaf(S[4 * i + 3], q4.w, acc1);
       }
-      part[(warp * kRetTok + tt) * kRetCols + lane] = acc0 + acc1;
+      part[(warp * TOK + tt) * kRetCols + lane] = acc0 + acc1;
     }
     __syncthreads();
     for (int tt = warp; tt < nt; tt += W) {
       float sum = 0.f;
 #pragma unroll
-      for (int w = 0; w < W; ++w) sum += part[(w * kRetTok + tt) * kRetCols + lane];
+      for (int w = 0; w < W; ++w) sum += part[(w * TOK + tt) * kRetCols + lane];
       if (col_ok) o[((row0 + t0 + tt) * H + h) * (int64_t)dv + c] = sum;
     }
     // the next block's staging writes qs / ks / vs (last read before the barrier above) and its
@@ -203,7 +204,7 @@ retention_kernel(float* __restrict__ o, const T* __restrict__ q, const T* __rest
   }
 }
 
-template <typename T, int W, int ROWS, bool ASYNC>
+template <typename T, int W, int ROWS, bool ASYNC, int TOK>
 int retention_launch(dim3 grid, size_t smem, cudaStream_t stream, float* o, const void* q, const void* k, const void* v,
                      float* state, const int64_t* req_pool_indices, const int64_t* seq_lens,
                      const int64_t* out_cache_loc, const int32_t* prefix_lens, const int32_t* extend_lens,
@@ -212,11 +213,11 @@ int retention_launch(dim3 grid, size_t smem, cudaStream_t stream, float* o, cons
                      float k_scale) {
   static size_t configured = 0;
   if (smem > 48 * 1024 && smem > configured) {
-    SPD_CUDA(cudaFuncSetAttribute(retention_kernel<T, W, ROWS, ASYNC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    SPD_CUDA(cudaFuncSetAttribute(retention_kernel<T, W, ROWS, ASYNC, TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   (int)smem));
     configured = smem;
   }
-  SPD_CUDA(launch(retention_kernel<T, W, ROWS, ASYNC>, grid, dim3(W * 32), smem, stream, /*pdl=*/false, o, (const T*)q,
+  SPD_CUDA(launch(retention_kernel<T, W, ROWS, ASYNC, TOK>, grid, dim3(W * 32), smem, stream, /*pdl=*/false, o, (const T*)q,
                   (const T*)k, (const T*)v, state, req_pool_indices, seq_lens, out_cache_loc, prefix_lens, extend_lens,
                   extend_start_loc, H, dk, dv, q_stride, k_stride, v_stride, decay, cos_sin, rot, max_positions,
                   k_scale));
@@ -247,10 +248,12 @@ int spd_retention(float* o, const void* q, const void* k, const void* v, float* 
   // warps x rows per thread covering head_dim: 8 rows per thread up to 128, 16 above
   const int warps = head_dim <= 32 ? 4 : head_dim <= 64 ? 8 : 16;
   const int dkp = head_dim <= 128 ? warps * 8 : 256;
-  const size_t smem = sizeof(float) * ((size_t)2 * kRetTok * dkp + kRetTok * kRetCols + (size_t)warps * kRetTok * kRetCols);
+  const bool decode = seq_lens != nullptr;
+  const size_t tok = decode ? 1 : kRetTok;
+  const size_t smem = sizeof(float) * ((size_t)2 * tok * dkp + tok * kRetCols + (size_t)warps * tok * kRetCols);
   // ragged extend with 16-byte aligned rows: the prefetching form
   const int vecn = dtype == SPD_F32 ? 4 : 8;
-  const bool async_ok = seq_lens == nullptr && head_dim % vecn == 0 && v_dim % vecn == 0 && q_stride % vecn == 0 &&
+  const bool async_ok = !decode && head_dim % vecn == 0 && v_dim % vecn == 0 && q_stride % vecn == 0 &&
                         k_stride % vecn == 0 && v_stride % vecn == 0 && rot_dims % 4 == 0 && aligned16(q) &&
                         aligned16(k) && aligned16(v) && (rot_dims == 0 || aligned16(cos_sin)) &&
                         getenv("SPD_RETENTION_SYNC") == nullptr;
@@ -261,8 +264,9 @@ int spd_retention(float* o, const void* q, const void* k, const void* v, float* 
       extend_start_loc, num_heads, head_dim, v_dim, q_stride, k_stride, v_stride, decay, cos_sin, rot_dims,       \
       max_positions, k_scale
 #define SPD_RET_SHAPE(W, ROWS)                                                                                    \
-  return async_ok ? retention_launch<T, W, ROWS, true>(grid, smem_async, SPD_RET_ARGS)                            \
-                  : retention_launch<T, W, ROWS, false>(grid, smem, SPD_RET_ARGS)
+  return decode     ? retention_launch<T, W, ROWS, false, 1>(grid, smem, SPD_RET_ARGS)                            \
+         : async_ok ? retention_launch<T, W, ROWS, true, kRetTok>(grid, smem_async, SPD_RET_ARGS)                 \
+                    : retention_launch<T, W, ROWS, false, kRetTok>(grid, smem, SPD_RET_ARGS)
   SPD_DISPATCH_ANY(dtype, {
     if (head_dim <= 32) SPD_RET_SHAPE(4, 8);
     else if (head_dim <= 64) SPD_RET_SHAPE(8, 8);
