@@ -359,8 +359,11 @@ int spd_act_and_mul(void* out, const void* x, int64_t rows, int64_t inter, int a
                     spd_stream_t stream);
 /* out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * silu(g[t, h, :]);  o fp32 [tokens, heads *
  * vdim] contiguous, g dtype with row stride g_stride, out dtype contiguous */
+/* w (nullable, dtype): a weight on the normed values, element h * w_head_stride + c for head h (stride 0:
+ * one vector of vdim shared by the heads) */
 int spd_headnorm_gate(void* out, const float* o, const void* g, int64_t tokens, int heads, int vdim,
-                      int64_t g_stride, float eps, int dtype, spd_stream_t stream);
+                      int64_t g_stride, float eps, const void* w, int w_head_stride, int dtype,
+                      spd_stream_t stream);
 /* C = A W^T on the CUDA cores with fp32 accumulation in ascending-k order (any M, N, K; any dtype).
  * tile_group != NULL: rows of A are grouped in 128-row tiles (spd_moe_align) and rows
  * [g * w_group_rows, +N) of W multiply the tiles of group g = tile_group[row / 128] (< 0: skipped). */
@@ -369,10 +372,13 @@ int spd_linear_simt(void* C, const void* A, const void* W, int64_t M, int64_t N,
                     int out_f32, spd_stream_t stream);
 /* Routing from fp32 logits (row stride ld): score = softmax (score_func 0) or sigmoid (1) of the logits,
  * the top_k largest scores are chosen (ties: smaller expert id), weights = score (renormalised over the
- * chosen ones if renormalize) x scale. */
+ * chosen ones if renormalize) x scale.
+ * correction (fp32 [experts], nullable) biases the SELECTION only (weights stay unbiased).  num_groups > 1: the
+ * experts are cut into equal runs of neighbours, a run ranks by its top-2 biased scores added together, and
+ * selection is restricted to the keep_groups highest-ranked runs. */
 int spd_moe_route_scores(int32_t* topk_ids, float* topk_w, const float* logits, int64_t ld, int64_t tokens,
                          int num_experts, int top_k, int score_func, int renormalize, float scale,
-                         spd_stream_t stream);
+                         const float* correction, int num_groups, int keep_groups, spd_stream_t stream);
 /* xs[r, :] = w(r) * x[row_token[r], :] with w(r) the routing weight of the entry sorted to row r (1 if
  * topk_w == NULL); zeros for padding rows — experts that weight their INPUT */
 int spd_moe_gather_scaled(void* xs, const void* x, const int32_t* row_token, const int32_t* inv_pos,
@@ -417,6 +423,60 @@ int spd_retention(float* o, const void* q, const void* k, const void* v, float* 
                   int64_t batch, int num_heads, int head_dim, int v_dim, int64_t q_stride, int64_t k_stride,
                   int64_t v_stride, const float* decay, const float* cos_sin, int rot_dims,
                   int64_t max_positions, float k_scale, int dtype, spd_stream_t stream);
+
+/* spd_residual_rmsnorm with a second weight: out2 = the same normed row times (weight_offset + w2)
+ * (out2 and w2 both NULL or both given) */
+int spd_residual_rmsnorm2(void* out, void* out2, float* x, const void* a, const void* b, const void* w,
+                          const void* w2, int64_t rows, int64_t dim, float eps, float weight_offset, int dtype,
+                          spd_stream_t stream);
+/* block-diagonal spd_linear_simt: for g < num_groups, C[:, g * c_group_cols : + N] =
+ * A[:, g * a_group_cols : + K] W[g * N : (g + 1) * N, :K]^T */
+int spd_linear_simt_block_diag(void* C, const void* A, const void* W, int64_t M, int64_t N, int64_t K,
+                               int64_t lda, int64_t ldw, int64_t ldc, int num_groups, int64_t a_group_cols,
+                               int64_t c_group_cols, int dtype, spd_stream_t stream);
+/* Linear attention with a decay per key channel that depends on the token; per head, state S [head_dim,
+ * v_dim] fp32 at slot req_pool_indices[r] (zero for a request that starts at position 0), written back.
+ *   form 0: w = sigmoid(z + z_bias)^(1 / tau);  S_t = diag(w_t) S_(t-1) + k_t v_t^T;  o_t = S_t^T (q_t q_scale)
+ *   form 1: w = exp(-exp(z + z_bias));  o_t = (S_(t-1) + diag(bonus[h]) k_t v_t^T)^T (q_t q_scale);
+ *           S_t = diag(w_t) S_(t-1) + k_t v_t^T
+ * q, k, z [tokens, heads * head_dim], v [tokens, heads * v_dim] (dtype, row strides given); z_bias (nullable)
+ * and bonus fp32 [heads * head_dim].  Decode / ragged extend and padded rows as spd_retention.  o fp32. */
+int spd_gated_recurrence(float* o, const void* q, const void* k, const void* v, const void* z, float* state,
+                         const int64_t* req_pool_indices, const int64_t* seq_lens, const int64_t* out_cache_loc,
+                         const int32_t* prefix_lens, const int32_t* extend_lens, const int32_t* extend_start_loc,
+                         int64_t batch, int num_heads, int head_dim, int v_dim, int64_t q_stride, int64_t k_stride,
+                         int64_t v_stride, int64_t z_stride, const float* z_bias, const float* bonus, int form,
+                         float q_scale, float tau, int dtype, spd_stream_t stream);
+/* out[s, t, :] = h[t, :] + (h[t - 1, :] - h[t, :]) * mu[s, :] for s < n_mix (out [n_mix, total_rows, dim]);
+ * the row before a request's first new row is shift_state[req_pool_indices[r]] (fp32 [slots, dim]; zeros at
+ * position 0), which then receives the request's last row.  max_rows_per_request: host-side bound of
+ * extend_lens (0: total_rows). */
+int spd_token_shift_mix(void* out, const void* h, const void* mu, float* shift_state,
+                        const int64_t* req_pool_indices, const int64_t* seq_lens, const int64_t* out_cache_loc,
+                        const int32_t* prefix_lens, const int32_t* extend_lens, const int32_t* extend_start_loc,
+                        int64_t batch, int64_t total_rows, int64_t max_rows_per_request, int64_t dim, int n_mix,
+                        int dtype, spd_stream_t stream);
+/* x[r, 2i] = table[idx[r], 2i] + sin(positions[r] f_i), x[r, 2i + 1] = table[idx[r], 2i + 1] + cos(positions[r] f_i),
+ * f_i = freq_hi[i] + freq_lo[i] (fp32 [ceil(dim / 2)] each) */
+int spd_embed_sincos(float* x, const void* table, const int64_t* idx, const int64_t* positions,
+                     const float* freq_hi, const float* freq_lo, int64_t rows, int64_t dim, int64_t table_rows,
+                     int dtype, spd_stream_t stream);
+/* out[r, :] = [a[r, :] | b[r, :]] converted to dtype (a, b fp32 [rows, dim]; out [rows, 2 dim]) */
+int spd_cast_concat(void* out, const float* a, const float* b, int64_t rows, int64_t dim, int dtype,
+                    spd_stream_t stream);
+/* out[r, c] = act(x[r * x_stride + c]); act 0 SiLU, 1 tanh-form GELU, 2 relu squared, 3 tanh, 4 relu */
+int spd_activation(void* out, const void* x, int64_t rows, int64_t cols, int64_t x_stride, int act, int dtype,
+                   spd_stream_t stream);
+/* y = x[r, :dim] / sqrt(mean(x[r, :dim]^2) + eps) * w; pool[loc[r] * pool_stride + :] = y (pool nullable) and
+ * out[r, :] = y (out nullable, contiguous) */
+int spd_rmsnorm_store(void* pool, void* out, const void* x, const void* w, const int64_t* loc, int64_t rows,
+                      int64_t dim, int64_t x_stride, int64_t pool_stride, float eps, int dtype,
+                      spd_stream_t stream);
+/* out[t, h, :] = o[t, h, :] * sigmoid(g[t, h]) (o row stride o_stride, g row stride g_stride, out contiguous) */
+int spd_head_gate_sigmoid(void* out, const void* o, const void* g, int64_t tokens, int heads, int vdim,
+                          int64_t o_stride, int64_t g_stride, int dtype, spd_stream_t stream);
+/* x[i] *= alpha for i < n */
+int spd_scale_f32(float* x, int64_t n, float alpha, spd_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -92,9 +92,23 @@ SIGNATURES = {
     "spd_residual_rmsnorm": (_i, [_p, _p, _p, _p, _p, _i64, _i64, _f, _f, _i, _p]),
     "spd_embed_f32": (_i, [_p, _p, _p, _i64, _i64, _i64, _i, _p]),
     "spd_act_and_mul": (_i, [_p, _p, _i64, _i64, _i, _i, _p]),
-    "spd_headnorm_gate": (_i, [_p, _p, _p, _i64, _i, _i, _i64, _f, _i, _p]),
+    "spd_headnorm_gate": (_i, [_p, _p, _p, _i64, _i, _i, _i64, _f, _p, _i, _i, _p]),
     "spd_linear_simt": (_i, [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _p, _i64, _i, _i, _p]),
-    "spd_moe_route_scores": (_i, [_p, _p, _p, _i64, _i64, _i, _i, _i, _i, _f, _p]),
+    "spd_moe_route_scores": (_i, [_p, _p, _p, _i64, _i64, _i, _i, _i, _i, _f, _p, _i, _i, _p]),
+    "spd_residual_rmsnorm2": (_i, [_p, _p, _p, _p, _p, _p, _p, _i64, _i64, _f, _f, _i, _p]),
+    "spd_linear_simt_block_diag": (_i, [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _i, _i64, _i64, _i, _p]),
+    "spd_gated_recurrence": (
+        _i,
+        [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i, _i, _i, _i64, _i64, _i64, _i64, _p, _p, _i, _f, _f,
+         _i, _p],
+    ),
+    "spd_token_shift_mix": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i, _i, _p]),
+    "spd_embed_sincos": (_i, [_p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i, _p]),
+    "spd_cast_concat": (_i, [_p, _p, _p, _i64, _i64, _i, _p]),
+    "spd_activation": (_i, [_p, _p, _i64, _i64, _i64, _i, _i, _p]),
+    "spd_rmsnorm_store": (_i, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _f, _i, _p]),
+    "spd_head_gate_sigmoid": (_i, [_p, _p, _p, _i64, _i, _i, _i64, _i64, _i, _p]),
+    "spd_scale_f32": (_i, [_p, _i64, _f, _p]),
     "spd_moe_gather_scaled": (_i, [_p, _p, _p, _p, _p, _i64, _i, _i64, _i64, _i, _p]),
     "spd_moe_combine_gated": (_i, [_p, _p, _p, _p, _p, _p, _i64, _i64, _i, _i64, _i, _p]),
     "spd_kv_store": (_i, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i, _p]),

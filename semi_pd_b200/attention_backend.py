@@ -116,6 +116,7 @@ class SpdAttnBackend(AttentionBackend):
             # hybrid family: every layer runs the general kernel or a retention mixer, neither of
             # which needs a workspace or a host-side plan
             self.impl = "general"
+            self.max_extend_len = 0
             return
         # "tc" = tcgen05 kernels (the product path, head_dim 128); "simt" exists for bring-up /
         # cross-checks and serves the head_dim-64 plumbing model (OPT-125m, BASELINE configs[0])
@@ -190,6 +191,32 @@ class SpdAttnBackend(AttentionBackend):
         return ops.retention(q, k, v, state, forward_batch.req_pool_indices,
                              prefix_lens=forward_batch.extend_prefix_lens, extend_lens=forward_batch.extend_seq_lens,
                              extend_start_loc=forward_batch.extend_start_loc, **common)
+
+    def _batch_rows(self, forward_batch: ForwardBatch) -> dict:
+        """The device-side description of a batch's rows that the recurrent kernels read."""
+        if forward_batch.forward_mode.is_decode():
+            return dict(seq_lens=forward_batch.seq_lens, out_cache_loc=forward_batch.out_cache_loc)
+        return dict(prefix_lens=forward_batch.extend_prefix_lens, extend_lens=forward_batch.extend_seq_lens,
+                    extend_start_loc=forward_batch.extend_start_loc)
+
+    def forward_gated_recurrence(self, q, k, v, z, layer, forward_batch: ForwardBatch):
+        """Linear-attention mixer with a per-token, per-key-channel decay over the request's state slot.
+        `layer` carries num_heads, head_dim, v_head_dim, layer_id, form ("sigmoid_pow" | "double_exp"), q_scale,
+        tau, z_bias and bonus (fp32 [heads · head_dim] or None).  → o fp32 [T, heads · v_head_dim]."""
+        state = forward_batch.token_to_kv_pool.state_pool.get_state(layer.layer_id)
+        return ops.gated_recurrence(q, k, v, z, state, forward_batch.req_pool_indices, num_heads=layer.num_heads,
+                                    head_dim=layer.head_dim, v_dim=layer.v_head_dim, form=layer.form,
+                                    q_scale=layer.q_scale, tau=layer.tau, z_bias=layer.z_bias, bonus=layer.bonus,
+                                    **self._batch_rows(forward_batch))
+
+    def forward_token_shift(self, h, mu, layer, forward_batch: ForwardBatch):
+        """Token shift of a mixer's input: → [n_mix, T, dim] = h + (previous row − h) · mu[s]; the row before a
+        request's first new one comes from (and its last row goes to) the layer's vector state slot."""
+        shift = forward_batch.token_to_kv_pool.state_pool.get_shift(layer.layer_id)
+        rows = self._batch_rows(forward_batch)
+        if not forward_batch.forward_mode.is_decode():
+            rows["max_extend_len"] = self.max_extend_len
+        return ops.token_shift_mix(h, mu, shift, forward_batch.req_pool_indices, **rows)
 
     def forward_extend(self, q, k, v, layer: RadixAttention, forward_batch: ForwardBatch,
                        save_kv_cache: bool = True):

@@ -64,6 +64,9 @@ class ModelConfig:
     # hybrid family (model_type "rimidra"): one entry per layer — {"type": "attention" | "retention",
     # "mixer": {...sizes and constants...}, "mlp": {...} | None, "weights_of": j (optional)}
     layer_specs: Optional[List[dict]] = None
+    # model_type "nupovik": layer_specs has one entry per layer RUN (a looped block repeats its layers, each
+    # run with a cache / state of its own); logits are multiplied by logit_scale
+    logit_scale: float = 1.0
 
     @property
     def context_len(self) -> int:
@@ -136,8 +139,49 @@ def _rimidra_config(path: str, cfg: dict, **overrides) -> ModelConfig:
     return ModelConfig(name=os.path.basename(os.path.normpath(path)) or "rimidra", **kw)
 
 
+_NUPOVIK_MIXERS = ("gla", "latent_attention", "wkv")
+
+
+def _nupovik_config(path: str, cfg: dict, **overrides) -> ModelConfig:
+    """config.json of the Nupovik family: {"architecture", "vocab", "width", "norm": {"eps"}, "logit_scale",
+    "layers": [{"type": "gla" | "latent_attention" | "wkv", "mixer": {...}, "mlp": {...} | null}, ...],
+    "loop": {"start", "stop", "times"}}.  The block of layers [start, stop) is executed `times` times back to back, re-using its
+    tensors; `layer_specs` lists the layer RUNS in execution order: "layer" is the index in the checkpoint's
+    names, "weights_of" the first run of the same layer (None for that run itself), "opens_pass" marks the
+    first layer of every pass of the loop (the stream is re-projected together with the embedding there)."""
+    layers = cfg["layers"]
+    for i, spec in enumerate(layers):
+        if spec["type"] not in _NUPOVIK_MIXERS:
+            raise ValueError(f"layer {i}: unknown mixer type {spec['type']!r}")
+        if spec.get("mlp") is not None and spec["mlp"].get("kind") not in ("dense", "moe"):
+            raise ValueError(f"layer {i}: unknown feed-forward kind {spec['mlp'].get('kind')!r}")
+    order = [(i, False) for i in range(len(layers))]
+    loop = cfg.get("loop") or None
+    if loop is not None:
+        a, b, n = int(loop["start"]), int(loop["stop"]), int(loop["times"])
+        if not (0 <= a < b <= len(layers)) or n < 1:
+            raise ValueError(f"loop {loop} does not fit {len(layers)} layers")
+        order = order[:a] + [(i, i == a) for _ in range(n) for i in range(a, b)] + order[b:]
+    runs, first = [], {}
+    for i, opens in order:
+        spec = dict(layers[i])
+        spec.update(layer=i, opens_pass=opens, weights_of=first.get(i))
+        first.setdefault(i, len(runs))
+        runs.append(spec)
+    heads = [int(s["mixer"]["heads"]) for s in runs]
+    kw = dict(model_type="nupovik", hidden_size=int(cfg["width"]), vocab_size=int(cfg["vocab"]),
+              num_hidden_layers=len(runs), rms_norm_eps=float(cfg["norm"]["eps"]), layer_specs=runs,
+              logit_scale=float(cfg.get("logit_scale", 1.0)),
+              # summary fields other components print or size by; the per-layer values rule
+              num_attention_heads=max(heads), num_key_value_heads=1,
+              head_dim=max(int(s["mixer"]["dim"]) for s in runs), intermediate_size=0,
+              max_position_embeddings=int(cfg.get("context", 8192)))
+    kw.update(overrides)
+    return ModelConfig(name=os.path.basename(os.path.normpath(path)) or "nupovik", **kw)
+
+
 # config.json "architecture" -> reader
-_ARCHITECTURE_READERS = {"Rimidra": _rimidra_config}
+_ARCHITECTURE_READERS = {"Rimidra": _rimidra_config, "Nupovik": _nupovik_config}
 
 
 def load_model_config(path: str, **overrides) -> ModelConfig:

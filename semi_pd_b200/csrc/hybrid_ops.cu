@@ -29,11 +29,13 @@ __device__ __forceinline__ float gelu_tanh_precise(float z) {
 }
 __device__ __forceinline__ float sigmoid_precise(float z) { return 1.0f / (1.0f + expf(-z)); }
 
-// one CTA per row: x += a (+ b); out = x * rsqrt(mean(x^2) + eps) * (off + w)
+// one CTA per row: x += a (+ b); out = x * rsqrt(mean(x^2) + eps) * (off + w); a second weight w2
+// gives a second normed copy out2 of the same row (layers whose two sublayers have a norm each)
 template <typename T>
 __global__ void __launch_bounds__(kRowThreads)
 residual_rmsnorm_kernel(T* __restrict__ out, float* __restrict__ x, const T* __restrict__ a,
-                        const T* __restrict__ b, const T* __restrict__ w, int64_t dim, float eps, float off) {
+                        const T* __restrict__ b, const T* __restrict__ w, int64_t dim, float eps, float off,
+                        T* __restrict__ out2, const T* __restrict__ w2) {
   griddep_wait();
   griddep_launch_dependents();
   __shared__ float red[kRowThreads / 32];
@@ -53,8 +55,11 @@ residual_rmsnorm_kernel(T* __restrict__ out, float* __restrict__ x, const T* __r
   ss = block_sum_256(ss, red);
   if (out == nullptr) return;
   const float inv = 1.0f / sqrtf(ss / (float)dim + eps);
-  for (int64_t i = threadIdx.x; i < dim; i += kRowThreads)
-    out[row * dim + i] = from_f32<T>(xr[i] * inv * (off + to_f32<T>(w[i])));
+  for (int64_t i = threadIdx.x; i < dim; i += kRowThreads) {
+    const float y = xr[i] * inv;
+    out[row * dim + i] = from_f32<T>(y * (off + to_f32<T>(w[i])));
+    if (out2 != nullptr) out2[row * dim + i] = from_f32<T>(y * (off + to_f32<T>(w2[i])));
+  }
 }
 
 template <typename T>
@@ -126,7 +131,7 @@ act_and_mul_kernel(T* __restrict__ out, const T* __restrict__ x, int64_t rows, i
 template <typename T>
 __global__ void __launch_bounds__(128)
 headnorm_gate_kernel(T* __restrict__ out, const float* __restrict__ o, const T* __restrict__ g, int64_t tokens,
-                     int heads, int vdim, int64_t g_stride, float eps) {
+                     int heads, int vdim, int64_t g_stride, float eps, const T* __restrict__ w, int w_head_stride) {
   griddep_wait();
   griddep_launch_dependents();
   const int lane = threadIdx.x & 31;
@@ -141,7 +146,8 @@ headnorm_gate_kernel(T* __restrict__ out, const float* __restrict__ o, const T* 
   const float inv = 1.0f / sqrtf(ss / (float)vdim + eps);
   for (int c = lane; c < vdim; c += 32) {
     const float gate = silu_precise(to_f32<T>(g[t * g_stride + (int64_t)h * vdim + c]));
-    out[(t * heads + h) * (int64_t)vdim + c] = from_f32<T>(orow[c] * inv * gate);
+    const float wt = w != nullptr ? to_f32<T>(w[h * w_head_stride + c]) : 1.f;
+    out[(t * heads + h) * (int64_t)vdim + c] = from_f32<T>(orow[c] * inv * wt * gate);
   }
 }
 
@@ -156,12 +162,17 @@ template <typename TA, typename TC>
 __global__ void __launch_bounds__(256)
 linear_simt_kernel(TC* __restrict__ C, const TA* __restrict__ A, const TA* __restrict__ W, int64_t M, int64_t N,
                    int64_t K, int64_t lda, int64_t ldw, int64_t ldc, const int32_t* __restrict__ tile_group,
-                   int64_t w_group_rows) {
+                   int64_t w_group_rows, int64_t a_group_cols, int64_t c_group_cols) {
   griddep_wait();
   griddep_launch_dependents();
   __shared__ __align__(16) float As[kSBK][kSPad];
   __shared__ __align__(16) float Ws[kSBK][kSPad];
   const int64_t m0 = (int64_t)blockIdx.y * kSBM, n0 = (int64_t)blockIdx.x * kSBN;
+  // block-diagonal form: block z multiplies columns [z * a_group_cols, + K) of A by rows
+  // [z * w_group_rows, + N) of W into columns [z * c_group_cols, + N) of C
+  A += (int64_t)blockIdx.z * a_group_cols;
+  C += (int64_t)blockIdx.z * c_group_cols;
+  if (tile_group == nullptr) W += (int64_t)blockIdx.z * w_group_rows * ldw;
   if (tile_group != nullptr) {
     const int g = tile_group[m0 / 128];
     if (g < 0) return;
@@ -212,23 +223,29 @@ linear_simt_kernel(TC* __restrict__ C, const TA* __restrict__ A, const TA* __res
 // routing from fp32 logits: one warp per token
 // ------------------------------------------------------------------------------------------------
 constexpr int kRouteMaxExperts = 256;
-constexpr int kRouteMaxTopK = 8;
+constexpr int kRouteMaxTopK = 16;
+constexpr int kRouteMaxGroups = 32;
 
+// scores s = sigmoid(z) or softmax(z); selection runs on the biased score c = s + correction.  With groups the
+// experts are cut into equal runs of neighbours, every run is ranked by its top-2 biased scores added together,
+// and experts outside the keep_groups highest-ranked runs are ineligible (c = -inf there).  The weight of a
+// selected expert is its unbiased s (optionally renormalised).
 __global__ void __launch_bounds__(128)
 moe_route_scores_kernel(int32_t* __restrict__ topk_ids, float* __restrict__ topk_w, const float* __restrict__ logits,
-                        int64_t ld, int64_t tokens, int E, int k, int score_func, int renorm, float scale) {
+                        int64_t ld, int64_t tokens, int E, int k, int score_func, int renorm, float scale,
+                        const float* __restrict__ correction, int num_groups, int keep_groups) {
   griddep_wait();
   griddep_launch_dependents();
   const int lane = threadIdx.x & 31;
   const int64_t t = blockIdx.x * 4ll + (threadIdx.x >> 5);
   if (t >= tokens) return;
   constexpr int PER = kRouteMaxExperts / 32;
-  float v[PER];
+  float v[PER];  // scores (0 outside the experts)
   if (score_func == 1) {
 #pragma unroll
     for (int i = 0; i < PER; ++i) {
       const int e = i * 32 + lane;
-      v[i] = e < E ? sigmoid_precise(logits[t * ld + e]) : -1.f;  // -1: not an expert / taken
+      v[i] = e < E ? sigmoid_precise(logits[t * ld + e]) : 0.f;
     }
   } else {
     float mx = -INFINITY;
@@ -242,13 +259,66 @@ moe_route_scores_kernel(int32_t* __restrict__ topk_ids, float* __restrict__ topk
     float sum = 0.f;
 #pragma unroll
     for (int i = 0; i < PER; ++i) {
-      v[i] = (i * 32 + lane) < E ? expf(v[i] - mx) : -1.f;
-      sum += fmaxf(v[i], 0.f);
+      v[i] = (i * 32 + lane) < E ? expf(v[i] - mx) : 0.f;
+      sum += v[i];
     }
     sum = warp_sum(sum);
 #pragma unroll
-    for (int i = 0; i < PER; ++i)
-      if (v[i] >= 0.f) v[i] = v[i] / sum;
+    for (int i = 0; i < PER; ++i) v[i] = v[i] / sum;
+  }
+  float c[PER];  // choice scores; -inf: not an expert, outside the kept groups, or taken
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int e = i * 32 + lane;
+    c[i] = e < E ? v[i] + (correction != nullptr ? correction[e] : 0.f) : -INFINITY;
+  }
+  if (num_groups > 1 && keep_groups < num_groups) {
+    const int per = E / num_groups;
+    float gscore = -INFINITY;  // lane g keeps the score of group g
+    for (int g = 0; g < num_groups; ++g) {
+      float a1 = -INFINITY, a2 = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < PER; ++i) {
+        const int e = i * 32 + lane;
+        if (e < E && e / per == g) {
+          if (c[i] > a1) { a2 = a1; a1 = c[i]; }
+          else if (c[i] > a2) a2 = c[i];
+        }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float b1 = __shfl_xor_sync(0xffffffffu, a1, o), b2 = __shfl_xor_sync(0xffffffffu, a2, o);
+        const float hi = fmaxf(a1, b1), lo = fmaxf(fminf(a1, b1), fmaxf(a2, b2));
+        a1 = hi;
+        a2 = lo;
+      }
+      if (lane == g) gscore = a1 + (per >= 2 ? a2 : 0.f);
+    }
+    unsigned kept = 0u;
+    for (int j = 0; j < keep_groups; ++j) {
+      float best = gscore;
+      int bg = lane < num_groups ? lane : 0x7fffffff;
+      if (lane >= num_groups) best = -INFINITY;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int og = __shfl_xor_sync(0xffffffffu, bg, o);
+        if (ob > best || (ob == best && og < bg)) { best = ob; bg = og; }
+      }
+      if (bg < num_groups) {
+        kept |= 1u << bg;
+        if (lane == bg) gscore = -INFINITY;
+      } else {
+        // every remaining group scores -inf (or NaN): keep the lowest one not yet kept
+        for (int g = 0; g < num_groups; ++g)
+          if (!((kept >> g) & 1u)) { kept |= 1u << g; if (lane == g) gscore = -INFINITY; break; }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      const int e = i * 32 + lane;
+      if (e < E && !((kept >> (e / per)) & 1u)) c[i] = -INFINITY;
+    }
   }
   float pw[kRouteMaxTopK];
   int pe[kRouteMaxTopK];
@@ -256,12 +326,12 @@ moe_route_scores_kernel(int32_t* __restrict__ topk_ids, float* __restrict__ topk
 #pragma unroll
   for (int j = 0; j < kRouteMaxTopK; ++j) {
     if (j < k) {
-      float best = -1.f;
+      float best = -INFINITY;
       int be = 0x7fffffff;
 #pragma unroll
       for (int i = 0; i < PER; ++i) {
         const int e = i * 32 + lane;
-        if (v[i] > best) { best = v[i]; be = e; }
+        if (c[i] > best) { best = c[i]; be = e; }
       }
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) {
@@ -269,16 +339,18 @@ moe_route_scores_kernel(int32_t* __restrict__ topk_ids, float* __restrict__ topk
         const int oe = __shfl_xor_sync(0xffffffffu, be, o);
         if (ob > best || (ob == best && oe < be)) { best = ob; be = oe; }
       }
-      pe[j] = be;
-      pw[j] = best;
-      wsum += best;
+      float w = 0.f;
 #pragma unroll
       for (int i = 0; i < PER; ++i)
-        if (i * 32 + lane == be) v[i] = -1.f;
+        if (i * 32 + lane == be) { w = v[i]; c[i] = -INFINITY; }
+      w = warp_sum(w);
+      pe[j] = be < E ? be : 0;
+      pw[j] = w;
+      wsum += w;
     }
   }
   if (lane == 0) {
-    const float f = renorm ? scale / wsum : scale;
+    const float f = renorm ? scale / (wsum + 1e-20f) : scale;
 #pragma unroll
     for (int j = 0; j < kRouteMaxTopK; ++j)
       if (j < k) {
@@ -380,7 +452,23 @@ int spd_residual_rmsnorm(void* out, float* x, const void* a, const void* b, cons
   if (rows == 0) return 0;
   SPD_DISPATCH_ANY(dtype, {
     SPD_CUDA(launch(residual_rmsnorm_kernel<T>, dim3((unsigned)rows), dim3(kRowThreads), 0, as_stream(stream),
-                    pdl_enabled(), (T*)out, x, (const T*)a, (const T*)b, (const T*)w, dim, eps, weight_offset));
+                    pdl_enabled(), (T*)out, x, (const T*)a, (const T*)b, (const T*)w, dim, eps, weight_offset,
+                    (T*)nullptr, (const T*)nullptr));
+  });
+  return 0;
+}
+
+int spd_residual_rmsnorm2(void* out, void* out2, float* x, const void* a, const void* b, const void* w,
+                          const void* w2, int64_t rows, int64_t dim, float eps, float weight_offset, int dtype,
+                          spd_stream_t stream) {
+  SPD_REQUIRE(x && out && w && (out2 == nullptr) == (w2 == nullptr), SPD_E_BADARG, "spd_residual_rmsnorm2: null pointer");
+  SPD_REQUIRE(rows >= 0 && dim > 0, SPD_E_BADARG, "spd_residual_rmsnorm2: bad sizes");
+  SPD_REQUIRE(a != nullptr || b == nullptr, SPD_E_BADARG, "spd_residual_rmsnorm2: b without a");
+  if (rows == 0) return 0;
+  SPD_DISPATCH_ANY(dtype, {
+    SPD_CUDA(launch(residual_rmsnorm_kernel<T>, dim3((unsigned)rows), dim3(kRowThreads), 0, as_stream(stream),
+                    pdl_enabled(), (T*)out, x, (const T*)a, (const T*)b, (const T*)w, dim, eps, weight_offset,
+                    (T*)out2, (const T*)w2));
   });
   return 0;
 }
@@ -420,14 +508,16 @@ int spd_act_and_mul(void* out, const void* x, int64_t rows, int64_t inter, int a
 }
 
 int spd_headnorm_gate(void* out, const float* o, const void* g, int64_t tokens, int heads, int vdim,
-                      int64_t g_stride, float eps, int dtype, spd_stream_t stream) {
+                      int64_t g_stride, float eps, const void* w, int w_head_stride, int dtype,
+                      spd_stream_t stream) {
   SPD_REQUIRE(out && o && g, SPD_E_BADARG, "spd_headnorm_gate: null pointer");
   SPD_REQUIRE(tokens >= 0 && heads > 0 && vdim > 0, SPD_E_BADARG, "spd_headnorm_gate: bad sizes");
   if (tokens == 0) return 0;
   const int64_t items = tokens * heads;
   SPD_DISPATCH_ANY(dtype, {
     SPD_CUDA(launch(headnorm_gate_kernel<T>, dim3((unsigned)((items + 3) / 4)), dim3(128), 0, as_stream(stream),
-                    pdl_enabled(), (T*)out, o, (const T*)g, tokens, heads, vdim, g_stride, eps));
+                    pdl_enabled(), (T*)out, o, (const T*)g, tokens, heads, vdim, g_stride, eps, (const T*)w,
+                    w_head_stride));
   });
   return 0;
 }
@@ -444,27 +534,50 @@ int spd_linear_simt(void* C, const void* A, const void* W, int64_t M, int64_t N,
   SPD_DISPATCH_ANY(dtype, {
     if (out_f32) {
       SPD_CUDA(launch(linear_simt_kernel<T, float>, grid, dim3(256), 0, as_stream(stream), pdl_enabled(), (float*)C,
-                      (const T*)A, (const T*)W, M, N, K, lda, ldw, ldc, tile_group, w_group_rows));
+                      (const T*)A, (const T*)W, M, N, K, lda, ldw, ldc, tile_group, w_group_rows, (int64_t)0,
+                      (int64_t)0));
     } else {
       SPD_CUDA(launch(linear_simt_kernel<T, T>, grid, dim3(256), 0, as_stream(stream), pdl_enabled(), (T*)C,
-                      (const T*)A, (const T*)W, M, N, K, lda, ldw, ldc, tile_group, w_group_rows));
+                      (const T*)A, (const T*)W, M, N, K, lda, ldw, ldc, tile_group, w_group_rows, (int64_t)0,
+                      (int64_t)0));
     }
+  });
+  return 0;
+}
+
+int spd_linear_simt_block_diag(void* C, const void* A, const void* W, int64_t M, int64_t N, int64_t K,
+                               int64_t lda, int64_t ldw, int64_t ldc, int num_groups, int64_t a_group_cols,
+                               int64_t c_group_cols, int dtype, spd_stream_t stream) {
+  SPD_REQUIRE(C && A && W, SPD_E_BADARG, "spd_linear_simt_block_diag: null pointer");
+  SPD_REQUIRE(M >= 0 && N > 0 && K > 0 && num_groups > 0 && num_groups <= 65535 && ldw >= K &&
+                  lda >= (num_groups - 1) * a_group_cols + K && ldc >= (num_groups - 1) * c_group_cols + N,
+              SPD_E_BADARG, "spd_linear_simt_block_diag: bad sizes M=%lld N=%lld K=%lld groups=%d", (long long)M,
+              (long long)N, (long long)K, num_groups);
+  if (M == 0) return 0;
+  const dim3 grid((unsigned)((N + kSBN - 1) / kSBN), (unsigned)((M + kSBM - 1) / kSBM), (unsigned)num_groups);
+  SPD_DISPATCH_ANY(dtype, {
+    SPD_CUDA(launch(linear_simt_kernel<T, T>, grid, dim3(256), 0, as_stream(stream), pdl_enabled(), (T*)C, (const T*)A,
+                    (const T*)W, M, N, K, lda, ldw, ldc, (const int32_t*)nullptr, N, a_group_cols, c_group_cols));
   });
   return 0;
 }
 
 int spd_moe_route_scores(int32_t* topk_ids, float* topk_w, const float* logits, int64_t ld, int64_t tokens,
                          int num_experts, int top_k, int score_func, int renormalize, float scale,
-                         spd_stream_t stream) {
+                         const float* correction, int num_groups, int keep_groups, spd_stream_t stream) {
   SPD_REQUIRE(topk_ids && topk_w && logits, SPD_E_BADARG, "spd_moe_route_scores: null pointer");
   SPD_REQUIRE(num_experts > 0 && num_experts <= kRouteMaxExperts && top_k > 0 && top_k <= kRouteMaxTopK &&
                   top_k <= num_experts && ld >= num_experts && (score_func == 0 || score_func == 1),
               SPD_E_SHAPE, "spd_moe_route_scores: experts %d (max %d), top_k %d (max %d)", num_experts,
               kRouteMaxExperts, top_k, kRouteMaxTopK);
+  SPD_REQUIRE(num_groups <= 1 || (num_groups <= kRouteMaxGroups && num_experts % num_groups == 0 && keep_groups >= 1 &&
+                                  keep_groups <= num_groups && (int64_t)keep_groups * (num_experts / num_groups) >= top_k),
+              SPD_E_SHAPE, "spd_moe_route_scores: %d groups (max %d, dividing the experts), keep %d", num_groups,
+              kRouteMaxGroups, keep_groups);
   if (tokens == 0) return 0;
   SPD_CUDA(launch(moe_route_scores_kernel, dim3((unsigned)((tokens + 3) / 4)), dim3(128), 0, as_stream(stream),
                   pdl_enabled(), topk_ids, topk_w, logits, ld, tokens, num_experts, top_k, score_func, renormalize,
-                  scale));
+                  scale, correction, num_groups, keep_groups));
   return 0;
 }
 

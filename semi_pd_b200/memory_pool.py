@@ -385,28 +385,41 @@ class RecurrentStatePool:
     `req_pool_idx` — the slot `ReqToTokenPool` hands out, so a state slot is taken, reused and freed
     with its request and needs no allocator of its own.  A kernel that starts a request at position
     0 ignores what the slot held before (no clearing on reuse).  `layer_shapes[l]` is (heads,
-    head_dim, v_dim) or None for layers without state."""
+    head_dim, v_dim) or None for layers without state.  `shift_dims[l]` (optional) is the row size of
+    a second, vector-valued state of layer l — the previous token's mixer input of a token-shift
+    mixer, `shift[l]` fp32 [slots, dim] — or None."""
 
-    def __init__(self, num_slots: int, layer_shapes: Sequence[Optional[Tuple[int, int, int]]], device: str):
+    def __init__(self, num_slots: int, layer_shapes: Sequence[Optional[Tuple[int, int, int]]], device: str,
+                 shift_dims: Optional[Sequence[Optional[int]]] = None):
         self.num_slots = num_slots
         self.layer_shapes = list(layer_shapes)
+        self.shift_dims = list(shift_dims) if shift_dims is not None else [None] * len(self.layer_shapes)
         self.device = device
         self.state: List[Optional[torch.Tensor]] = [
             torch.zeros((num_slots,) + tuple(s), dtype=torch.float32, device=device) if s is not None else None
             for s in self.layer_shapes]
+        self.shift: List[Optional[torch.Tensor]] = [
+            torch.zeros((num_slots, int(d)), dtype=torch.float32, device=device) if d else None
+            for d in self.shift_dims]
 
     @staticmethod
-    def bytes_per_slot(layer_shapes: Sequence[Optional[Tuple[int, int, int]]]) -> int:
-        return sum(4 * s[0] * s[1] * s[2] for s in layer_shapes if s is not None)
+    def bytes_per_slot(layer_shapes: Sequence[Optional[Tuple[int, int, int]]],
+                       shift_dims: Optional[Sequence[Optional[int]]] = None) -> int:
+        return (sum(4 * s[0] * s[1] * s[2] for s in layer_shapes if s is not None)
+                + sum(4 * int(d) for d in (shift_dims or []) if d))
 
     def get_state(self, layer_id: int) -> torch.Tensor:
         return self.state[layer_id]
+
+    def get_shift(self, layer_id: int) -> torch.Tensor:
+        return self.shift[layer_id]
 
 
 class HybridTokenToKVPool(KVCache):
     """KV pool of a model whose layers differ: layer l with `layer_shapes[l]` = (kv_heads, k_dim,
     v_dim) owns k_buffer[l] [size + 1, kv_heads, k_dim] and v_buffer[l] [size + 1, kv_heads, v_dim]
-    (key and value sizes may differ); layers with None (recurrent mixers) own nothing here.  All
+    (key and value sizes may differ; v_dim 0: values are read from the key rows themselves — one
+    latent buffer, `v_buffer[l] is k_buffer[l]`); layers with None (recurrent mixers) own nothing here.  All
     layers share the slot ids of one TokenToKVPoolAllocator, as in MHATokenToKVPool.  `dtype` may be
     float32.  The recurrent layers' state pool travels with this object (`state_pool`), so both
     workers of a GPU see it through the one pool they already share."""
@@ -429,7 +442,8 @@ class HybridTokenToKVPool(KVCache):
         self.v_buffer: List[Optional[torch.Tensor]] = []
         for s in self.layer_shapes:
             self.k_buffer.append(torch.zeros((rows, s[0], s[1]), dtype=dtype, device=device) if s else None)
-            self.v_buffer.append(torch.zeros((rows, s[0], s[2]), dtype=dtype, device=device) if s else None)
+            self.v_buffer.append(None if not s else self.k_buffer[-1] if s[2] == 0 else
+                                 torch.zeros((rows, s[0], s[2]), dtype=dtype, device=device))
 
     @staticmethod
     def bytes_per_token(layer_shapes, dtype: torch.dtype) -> int:
@@ -438,7 +452,8 @@ class HybridTokenToKVPool(KVCache):
 
     def get_kv_size_bytes(self):
         k = sum(b.numel() * b.element_size() for b in self.k_buffer if b is not None)
-        v = sum(b.numel() * b.element_size() for b in self.v_buffer if b is not None)
+        v = sum(b.numel() * b.element_size() for b, kb in zip(self.v_buffer, self.k_buffer)
+                if b is not None and b is not kb)
         return k, v
 
     def get_key_buffer(self, layer_id: int):
@@ -454,4 +469,6 @@ class HybridTokenToKVPool(KVCache):
                       k_scale=None, v_scale=None):
         if cache_k.dtype != self.dtype:
             raise RuntimeError("KV cache dtype conversion is not on the semi-PD path")
-        ops.kv_store(cache_k, cache_v, self.k_buffer[layer.layer_id], self.v_buffer[layer.layer_id], loc)
+        shared = self.v_buffer[layer.layer_id] is self.k_buffer[layer.layer_id]
+        ops.kv_store(cache_k, None if shared else cache_v, self.k_buffer[layer.layer_id],
+                     self.v_buffer[layer.layer_id], loc)

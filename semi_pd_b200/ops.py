@@ -577,15 +577,22 @@ def act_and_mul(x: torch.Tensor, act: str = "silu") -> torch.Tensor:
     return out
 
 
-def headnorm_gate(o: torch.Tensor, gate: torch.Tensor, heads: int, vdim: int, eps: float) -> torch.Tensor:
-    """o fp32 [T, heads·vdim] → per-head o / rms(o) · silu(gate), in gate's dtype."""
-    _cuda(o, gate)
+def headnorm_gate(o: torch.Tensor, gate: torch.Tensor, heads: int, vdim: int, eps: float,
+                  weight: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """o fp32 [T, heads·vdim] → per-head o / rms(o) [· weight] · silu(gate), in gate's dtype.  weight: [vdim]
+    (shared by the heads) or [heads·vdim], in gate's dtype."""
+    _cuda(o, gate, weight)
+    w_stride = 0
+    if weight is not None:
+        if weight.dtype != gate.dtype or not weight.is_contiguous() or weight.numel() not in (vdim, heads * vdim):
+            raise RuntimeError("headnorm_gate: weight is [vdim] or [heads * vdim] in the gate's dtype")
+        w_stride = vdim if weight.numel() == heads * vdim and heads > 1 else 0
     if o.dtype != torch.float32 or not o.is_contiguous() or gate.stride(1) != 1:
         raise RuntimeError("headnorm_gate: o is contiguous fp32, gate has contiguous rows")
     T = o.shape[0]
     out = torch.empty((T, heads * vdim), device=o.device, dtype=gate.dtype)
     check(lib.spd_headnorm_gate(out.data_ptr(), o.data_ptr(), gate.data_ptr(), T, heads, vdim, gate.stride(0),
-                                float(eps), _dta(gate), _stream()), "spd_headnorm_gate")
+                                float(eps), _ptr(weight), w_stride, _dta(gate), _stream()), "spd_headnorm_gate")
     return out
 
 
@@ -649,9 +656,15 @@ def linear_silu_mul_any(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
 
 
 def moe_route_scores(logits: torch.Tensor, num_experts: int, top_k: int, score_func: str = "sigmoid",
-                     renormalize: bool = False, scale: float = 1.0):
-    """fp32 logits [T, >= E] (row stride free) → (topk_ids int32 [T, k], topk_weights fp32 [T, k])."""
-    _cuda(logits)
+                     renormalize: bool = False, scale: float = 1.0, correction: Optional[torch.Tensor] = None,
+                     num_groups: int = 1, keep_groups: int = 1):
+    """fp32 logits [T, >= E] (row stride free) → (topk_ids int32 [T, k], topk_weights fp32 [T, k]).
+    correction (fp32 [E]) biases the selection, never the weights; with num_groups > 1 the experts are cut into
+    equal runs, each run is ranked by its top-2 biased scores added together, and selection is restricted to the
+    keep_groups highest-ranked runs."""
+    _cuda(logits, correction)
+    if correction is not None and (correction.dtype != torch.float32 or correction.numel() != num_experts):
+        raise RuntimeError("moe_route_scores: correction is fp32 [experts]")
     if logits.dtype != torch.float32 or logits.stride(1) != 1:
         raise RuntimeError("moe_route_scores: logits are fp32 with contiguous rows")
     T = logits.shape[0]
@@ -659,7 +672,8 @@ def moe_route_scores(logits: torch.Tensor, num_experts: int, top_k: int, score_f
     w = torch.empty((T, top_k), device=logits.device, dtype=torch.float32)
     check(lib.spd_moe_route_scores(ids.data_ptr(), w.data_ptr(), logits.data_ptr(), logits.stride(0), T, num_experts,
                                    top_k, {"softmax": 0, "sigmoid": 1}[score_func], 1 if renormalize else 0,
-                                   float(scale), _stream()), "spd_moe_route_scores")
+                                   float(scale), _ptr(correction), int(num_groups), int(keep_groups), _stream()),
+          "spd_moe_route_scores")
     return ids, w
 
 
@@ -691,12 +705,185 @@ def moe_combine_gated(y: torch.Tensor, inv_pos: torch.Tensor, tokens: int, top_k
     return out
 
 
+def residual_rmsnorm2(x: torch.Tensor, weight: torch.Tensor, weight2: Optional[torch.Tensor], eps: float,
+                      a: Optional[torch.Tensor] = None, b: Optional[torch.Tensor] = None, weight_offset: float = 0.0):
+    """x (fp32, in place) += a (+ b); → (norm(x) · (off + weight), norm(x) · (off + weight2) or None): one
+    pass over the row for layers whose two sublayers have a norm weight each."""
+    _cuda(x, weight, weight2, a, b)
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise RuntimeError("residual_rmsnorm2: the residual stream is contiguous fp32")
+    for t in (a, b):
+        if t is not None and (not t.is_contiguous() or t.shape != x.shape or t.dtype != weight.dtype):
+            raise RuntimeError("residual_rmsnorm2: a / b must match x, be contiguous and share the weight's dtype")
+    if weight2 is not None and weight2.dtype != weight.dtype:
+        raise RuntimeError("residual_rmsnorm2: the two weights share a dtype")
+    d = x.shape[-1]
+    out = torch.empty(x.shape, device=x.device, dtype=weight.dtype)
+    out2 = torch.empty_like(out) if weight2 is not None else None
+    check(lib.spd_residual_rmsnorm2(out.data_ptr(), _ptr(out2), x.data_ptr(), _ptr(a), _ptr(b), weight.data_ptr(),
+                                    _ptr(weight2), x.numel() // d, d, float(eps), float(weight_offset), _dta(weight),
+                                    _stream()), "spd_residual_rmsnorm2")
+    return out, out2
+
+
+def linear_block_diag_any(x: torch.Tensor, weight: torch.Tensor, num_groups: int, k: int, n: int) -> torch.Tensor:
+    """out[:, g n : (g + 1) n] = x[:, g k : (g + 1) k] @ weight[g n : (g + 1) n, :k].T for g < num_groups — the
+    per-head products of an absorbed latent attention; tensor cores where the shapes tile, CUDA cores otherwise."""
+    _cuda(x, weight)
+    if x.dim() != 2 or weight.dim() != 2 or x.stride(1) != 1 or weight.stride(1) != 1 or x.dtype != weight.dtype:
+        raise RuntimeError("linear_block_diag_any: x and weight must be 2-D, contiguous rows, same dtype")
+    if (x.dtype in _DTYPE and n % 128 == 0 and k % 64 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
+            and weight.data_ptr() % 16 == 0 and os.environ.get("SPD_HYBRID_GEMM", "tc") == "tc"):
+        return linear_block_diag(x, weight, num_groups, k, n, x_group_stride=k, out_group_stride=n)
+    M = x.shape[0]
+    out = torch.empty((M, num_groups * n), device=x.device, dtype=x.dtype)
+    check(lib.spd_linear_simt_block_diag(out.data_ptr(), x.data_ptr(), weight.data_ptr(), M, n, k, x.stride(0),
+                                         weight.stride(0), out.stride(0), num_groups, k, n, _dta(x), _stream()),
+          "spd_linear_simt_block_diag")
+    return out
+
+
+def gated_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor, state: torch.Tensor,
+                     req_pool_indices, num_heads: int, head_dim: int, v_dim: int, form: str, q_scale: float = 1.0,
+                     tau: float = 1.0, z_bias: Optional[torch.Tensor] = None, bonus: Optional[torch.Tensor] = None,
+                     seq_lens=None, out_cache_loc=None, prefix_lens=None, extend_lens=None,
+                     extend_start_loc=None) -> torch.Tensor:
+    """Linear attention with a per-token decay per key channel over the per-request state (updated in place).
+    form "sigmoid_pow": w = sigmoid(z + z_bias)^(1/tau), o_t reads the updated state; form "double_exp":
+    w = exp(-exp(z + z_bias)), o_t reads the old state plus bonus · k_t v_tᵀ.  q / k / z [T, H·head_dim],
+    v [T, H·v_dim] (row-strided views allowed) → o fp32 [T, H·v_dim]."""
+    _cuda(q, k, v, z, state, req_pool_indices, z_bias, bonus)
+    T = q.shape[0]
+    if state.dtype != torch.float32 or not state.is_contiguous():
+        raise RuntimeError("gated_recurrence: the state is contiguous fp32")
+    if any(t.stride(1) != 1 for t in (q, k, v, z)) or not (q.dtype == k.dtype == v.dtype == z.dtype):
+        raise RuntimeError("gated_recurrence: q / k / v / z need contiguous rows and one dtype")
+    for t in (z_bias, bonus):
+        if t is not None and (t.dtype != torch.float32 or t.numel() != num_heads * head_dim or not t.is_contiguous()):
+            raise RuntimeError("gated_recurrence: z_bias and bonus are fp32 [heads * head_dim]")
+    o = torch.empty((T, num_heads * v_dim), device=q.device, dtype=torch.float32)
+    check(lib.spd_gated_recurrence(o.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), z.data_ptr(),
+                                   state.data_ptr(), req_pool_indices.data_ptr(), _ptr(seq_lens), _ptr(out_cache_loc),
+                                   _ptr(prefix_lens), _ptr(extend_lens), _ptr(extend_start_loc),
+                                   req_pool_indices.numel(), num_heads, head_dim, v_dim, q.stride(0), k.stride(0),
+                                   v.stride(0), z.stride(0), _ptr(z_bias), _ptr(bonus),
+                                   {"sigmoid_pow": 0, "double_exp": 1}[form], float(q_scale), float(tau), _dta(q),
+                                   _stream()), "spd_gated_recurrence")
+    return o
+
+
+def token_shift_mix(h: torch.Tensor, mu: torch.Tensor, shift_state: torch.Tensor, req_pool_indices, seq_lens=None,
+                    out_cache_loc=None, prefix_lens=None, extend_lens=None, extend_start_loc=None,
+                    max_extend_len: int = 0) -> torch.Tensor:
+    """→ [n_mix, T, dim]: h + (previous row − h) · mu[s]; a request's row before its first new one is kept in
+    shift_state[slot] (fp32 [slots, dim], zeros at position 0), which then receives its last row."""
+    _cuda(h, mu, shift_state, req_pool_indices)
+    if h.dim() != 2 or not h.is_contiguous() or mu.dtype != h.dtype or not mu.is_contiguous() or mu.shape[1] != h.shape[1]:
+        raise RuntimeError("token_shift_mix: h [T, dim] and mu [n_mix, dim] are contiguous and share a dtype")
+    if shift_state.dtype != torch.float32 or not shift_state.is_contiguous():
+        raise RuntimeError("token_shift_mix: the shift state is contiguous fp32")
+    T, dim = h.shape
+    out = torch.empty((mu.shape[0], T, dim), device=h.device, dtype=h.dtype)
+    check(lib.spd_token_shift_mix(out.data_ptr(), h.data_ptr(), mu.data_ptr(), shift_state.data_ptr(),
+                                  req_pool_indices.data_ptr(), _ptr(seq_lens), _ptr(out_cache_loc), _ptr(prefix_lens),
+                                  _ptr(extend_lens), _ptr(extend_start_loc), req_pool_indices.numel(), T,
+                                  int(max_extend_len), dim, mu.shape[0], _dta(h), _stream()), "spd_token_shift_mix")
+    return out
+
+
+def embed_sincos(table: torch.Tensor, idx: torch.Tensor, positions: torch.Tensor, freq_hi: torch.Tensor,
+                 freq_lo: torch.Tensor) -> torch.Tensor:
+    """fp32 [n, dim]: table rows plus the sinusoidal position vector (sin at even, cos at odd entries of
+    position · (freq_hi + freq_lo)[i])."""
+    _cuda(table, idx, positions, freq_hi, freq_lo)
+    if idx.dtype != torch.int64:
+        idx = idx.long()
+    if positions.dtype != torch.int64:
+        positions = positions.long()
+    out = torch.empty((idx.numel(), table.shape[1]), device=table.device, dtype=torch.float32)
+    check(lib.spd_embed_sincos(out.data_ptr(), table.data_ptr(), idx.data_ptr(), positions.data_ptr(),
+                               freq_hi.data_ptr(), freq_lo.data_ptr(), idx.numel(), table.shape[1], table.shape[0],
+                               _dta(table), _stream()), "spd_embed_sincos")
+    return out
+
+
+def cast_concat(a: torch.Tensor, b: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """[a | b] of two fp32 [T, dim] streams in `dtype` — the operand of a projection that reads both."""
+    _cuda(a, b)
+    if a.dtype != torch.float32 or b.dtype != torch.float32 or a.shape != b.shape or not a.is_contiguous() \
+            or not b.is_contiguous():
+        raise RuntimeError("cast_concat: a and b are contiguous fp32 of one shape")
+    out = torch.empty((a.shape[0], 2 * a.shape[1]), device=a.device, dtype=dtype)
+    check(lib.spd_cast_concat(out.data_ptr(), a.data_ptr(), b.data_ptr(), a.shape[0], a.shape[1], _dta(out), _stream()),
+          "spd_cast_concat")
+    return out
+
+
+_ACTS = {"silu": 0, "gelu_tanh": 1, "relu2": 2, "tanh": 3, "relu": 4}
+
+
+def activation(x: torch.Tensor, act: str) -> torch.Tensor:
+    """act(x) elementwise (silu, gelu_tanh, relu2 = relu squared, tanh, relu); x [rows, cols] with contiguous rows."""
+    _cuda(x)
+    if x.dim() != 2 or x.stride(1) != 1:
+        raise RuntimeError("activation: x must be [rows, cols] with contiguous rows")
+    out = torch.empty(x.shape, device=x.device, dtype=x.dtype)
+    check(lib.spd_activation(out.data_ptr(), x.data_ptr(), x.shape[0], x.shape[1], x.stride(0), _ACTS[act], _dta(x),
+                             _stream()), "spd_activation")
+    return out
+
+
+def rmsnorm_store(x: torch.Tensor, weight: torch.Tensor, eps: float, pool: Optional[torch.Tensor] = None,
+                  loc: Optional[torch.Tensor] = None, want_out: bool = False) -> Optional[torch.Tensor]:
+    """RMS norm of the rows of x (row-strided view allowed) times weight, written to pool[loc[t]] (a cache pool
+    whose rows are at least as long) and / or returned."""
+    _cuda(x, weight, pool, loc)
+    if x.dim() != 2 or x.stride(1) != 1 or weight.dtype != x.dtype or (pool is not None and pool.dtype != x.dtype):
+        raise RuntimeError("rmsnorm_store: x [T, dim] with contiguous rows; weight and pool in x's dtype")
+    if pool is not None and loc.dtype != torch.int64:
+        loc = loc.long()
+    T, dim = x.shape
+    out = torch.empty((T, dim), device=x.device, dtype=x.dtype) if want_out else None
+    pool_stride = pool.stride(0) if pool is not None else 0
+    check(lib.spd_rmsnorm_store(_ptr(pool), _ptr(out), x.data_ptr(), weight.data_ptr(), _ptr(loc), T, dim, x.stride(0),
+                                pool_stride, float(eps), _dta(x), _stream()), "spd_rmsnorm_store")
+    return out
+
+
+def head_gate_sigmoid(o: torch.Tensor, g: torch.Tensor, heads: int, vdim: int) -> torch.Tensor:
+    """o [T, heads·vdim] · sigmoid(g [T, heads]) per head (row-strided views allowed)."""
+    _cuda(o, g)
+    if o.stride(1) != 1 or g.stride(1) != 1 or o.dtype != g.dtype:
+        raise RuntimeError("head_gate_sigmoid: o and g need contiguous rows and one dtype")
+    T = o.shape[0]
+    out = torch.empty((T, heads * vdim), device=o.device, dtype=o.dtype)
+    check(lib.spd_head_gate_sigmoid(out.data_ptr(), o.data_ptr(), g.data_ptr(), T, heads, vdim, o.stride(0),
+                                    g.stride(0), _dta(o), _stream()), "spd_head_gate_sigmoid")
+    return out
+
+
+def scale_f32_(x: torch.Tensor, alpha: float) -> torch.Tensor:
+    """x *= alpha in place (contiguous fp32)."""
+    _cuda(x)
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise RuntimeError("scale_f32_: x is contiguous fp32")
+    check(lib.spd_scale_f32(x.data_ptr(), x.numel(), float(alpha), _stream()), "spd_scale_f32")
+    return x
+
+
 def kv_store(key: torch.Tensor, value: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
              loc: torch.Tensor) -> None:
     """k_pool[loc] = key rows, v_pool[loc] = value rows (row sizes may differ; any dtype)."""
     _cuda(key, value, k_pool, v_pool, loc)
     T = key.shape[0]
     if T == 0:
+        return
+    if value is None:  # one buffer holds keys and values (a latent cache)
+        k2 = key.reshape(T, -1)
+        if loc.dtype != torch.int64:
+            loc = loc.long()
+        check(lib.spd_kv_store(k2.data_ptr(), None, k_pool.data_ptr(), None, loc.data_ptr(), T, k2.shape[1], 0,
+                               k2.stride(0), 0, _dta(key), _stream()), "spd_kv_store")
         return
     k2, v2 = key.reshape(T, -1), value.reshape(T, -1)  # views for row-strided slices of a merged projection
     if k2.dim() != 2 or v2.dim() != 2 or k2.stride(1) != 1 or v2.stride(1) != 1:

@@ -11,6 +11,7 @@ _MODELS: Dict[str, Tuple[str, str]] = {
     "opt": ("opt", "OPTForCausalLM"),
     "deepseek_v2": ("deepseek_v2", "DeepseekV2ForCausalLM"),
     "rimidra": ("rimidra", "RimidraForCausalLM"),
+    "nupovik": ("nupovik", "NupovikForCausalLM"),
 }
 
 
