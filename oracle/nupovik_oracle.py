@@ -32,11 +32,11 @@ def relu_sq(x):
 def position_vector(positions, width):
     """[n, width]: even entries sin(p f_i), odd entries cos(p f_i), f_i = 10000^(-2 i / width)."""
     p = torch.as_tensor(positions, dtype=F64).reshape(-1, 1)
-    i = torch.arange(width // 2, dtype=F64)
+    i = torch.arange((width + 1) // 2, dtype=F64)
     ang = p * torch.pow(torch.tensor(10000.0, dtype=F64), -2.0 * i / width)
     out = torch.zeros(p.shape[0], width, dtype=F64)
     out[:, 0::2] = ang.sin()
-    out[:, 1::2] = ang.cos()
+    out[:, 1::2] = ang.cos()[:, : width // 2]
     return out
 
 
@@ -44,6 +44,40 @@ def embed(w, tokens, first_position=0):
     E = f64(w["embed"])
     tok = torch.as_tensor(tokens, dtype=torch.long)
     return E[tok] + position_vector(range(first_position, first_position + len(tok)), E.shape[1])
+
+
+# ---- recurrences ---------------------------------------------------------------------------------
+def sigmoid_pow_decay(z, tau):
+    return torch.sigmoid(z).pow(1.0 / tau)
+
+
+def double_exp_decay(z):
+    return torch.exp(-torch.exp(z))
+
+
+def decay_recurrence(q, k, v, w, S):
+    """q, k, w [T, H, dk], v [T, H, dv], S [H, dk, dv]: S <- diag(w_t) S + k_t v_tᵀ, o_t = Sᵀ q_t (the new S)."""
+    o = torch.zeros(q.shape[0], q.shape[1], v.shape[2], dtype=F64)
+    for t in range(q.shape[0]):
+        S = w[t].unsqueeze(-1) * S + k[t].unsqueeze(-1) * v[t].unsqueeze(-2)
+        o[t] = torch.einsum("hkv,hk->hv", S, q[t])
+    return o, S
+
+
+def bonus_recurrence(r, k, v, w, u, S):
+    """o_t = (S + diag(u) k_t v_tᵀ)ᵀ r_t with the old S, then S <- diag(w_t) S + k_t v_tᵀ.  u [H, dk]."""
+    o = torch.zeros(r.shape[0], r.shape[1], v.shape[2], dtype=F64)
+    for t in range(r.shape[0]):
+        kv = k[t].unsqueeze(-1) * v[t].unsqueeze(-2)
+        o[t] = torch.einsum("hkv,hk->hv", S + u.unsqueeze(-1) * kv, r[t])
+        S = w[t].unsqueeze(-1) * S + kv
+    return o, S
+
+
+def token_shift(h, prev, mu):
+    """h [T, W], prev [W] (the row before h[0]), mu [n, W] → [n, T, W]."""
+    shifted = torch.cat([prev.view(1, -1), h[:-1]], 0)
+    return h.unsqueeze(0) + (shifted - h).unsqueeze(0) * mu.unsqueeze(1)
 
 
 # ---- mixers --------------------------------------------------------------------------------------
@@ -55,12 +89,9 @@ def gla_mixer(h, w, p, m, eps, state=None):
     k = (h @ f64(w[p + "k"]).T).view(T, H, dk)
     v = (h @ f64(w[p + "v"]).T).view(T, H, dv)
     z = (h @ f64(w[p + "a1"]).T) @ f64(w[p + "a2"]).T + f64(w[p + "a2.b"])
-    alpha = torch.sigmoid(z).pow(1.0 / tau).view(T, H, dk)
+    alpha = sigmoid_pow_decay(z, tau).view(T, H, dk)
     S = torch.zeros(H, dk, dv, dtype=F64) if state is None else state.clone()
-    o = torch.zeros(T, H, dv, dtype=F64)
-    for t in range(T):
-        S = alpha[t].unsqueeze(-1) * S + k[t].unsqueeze(-1) * v[t].unsqueeze(-2)
-        o[t] = torch.einsum("hkv,hk->hv", S, q[t])
+    o, S = decay_recurrence(q, k, v, alpha, S)
     o = rms_norm(o, w[p + "norm"], eps).reshape(T, H * dv)
     return (o * silu(h @ f64(w[p + "g"]).T)) @ f64(w[p + "o"]).T, S
 
@@ -92,23 +123,17 @@ def wkv_mixer(h, w, p, m, eps, state=None):
     T, width = h.shape
     S, prev = (torch.zeros(H, dk, dk, dtype=F64), torch.zeros(width, dtype=F64)) if state is None else \
         (state[0].clone(), state[1].clone())
-    shifted = torch.cat([prev.view(1, -1), h[:-1]], 0)
+    mixes = token_shift(h, prev, torch.stack([f64(w[p + "mu." + s]) for s in "rkvgw"]))
 
     def mixed(s):
-        return h + (shifted - h) * f64(w[p + "mu." + s])
+        return mixes["rkvgw".index(s)]
 
     r = (mixed("r") @ f64(w[p + "r"]).T).view(T, H, dk)
     k = (mixed("k") @ f64(w[p + "k"]).T).view(T, H, dk)
     v = (mixed("v") @ f64(w[p + "v"]).T).view(T, H, dk)
     gate = silu(mixed("g") @ f64(w[p + "g"]).T)
-    dec = torch.exp(-torch.exp(torch.tanh(mixed("w") @ f64(w[p + "w1"]).T) @ f64(w[p + "w2"]).T + f64(w[p + "w0"])))
-    dec = dec.view(T, H, dk)
-    u = f64(w[p + "u"]).view(H, dk)
-    o = torch.zeros(T, H, dk, dtype=F64)
-    for t in range(T):
-        kv = k[t].unsqueeze(-1) * v[t].unsqueeze(-2)
-        o[t] = torch.einsum("hkv,hk->hv", S + u.unsqueeze(-1) * kv, r[t])
-        S = dec[t].unsqueeze(-1) * S + kv
+    dec = double_exp_decay(torch.tanh(mixed("w") @ f64(w[p + "w1"]).T) @ f64(w[p + "w2"]).T + f64(w[p + "w0"]))
+    o, S = bonus_recurrence(r, k, v, dec.view(T, H, dk), f64(w[p + "u"]).view(H, dk), S)
     o = rms_norm(o, None, eps).reshape(T, H * dk) * f64(w[p + "norm"])
     return (o * gate) @ f64(w[p + "o"]).T, (S, h[-1].clone())
 
@@ -120,10 +145,14 @@ def dense_ff(h, w, p):
 
 def route(h, w, p, r):
     """→ (ids [T, top], weights [T, top]) of the grouped sigmoid router."""
+    return route_logits(h @ f64(w[p + "router"]).T, f64(w[p + "correction"]), r)
+
+
+def route_logits(z, correction, r):
     E, top = int(r["experts"]), int(r["top"])
     G, keep = int(r["groups"]["count"]), int(r["groups"]["keep"])
-    s = torch.sigmoid(h @ f64(w[p + "router"]).T)
-    choice = s + f64(w[p + "correction"])
+    s = torch.sigmoid(z)
+    choice = s + correction
     per = E // G
     grouped = choice.view(-1, G, per)
     gscore = grouped.topk(min(2, per), -1).values.sum(-1)
@@ -195,3 +224,87 @@ class Stepper:
 
 def forward(cfg, w, tokens, residuals=None):
     return Stepper(cfg, w).feed(tokens, residuals)
+
+
+# ---- configurations and random checkpoints for tests ---------------------------------------------
+def dense_mlp(ff):
+    return {"kind": "dense", "ff": ff}
+
+
+def moe_mlp(experts, top, ff, groups=1, keep=1):
+    return {"kind": "moe", "expert": {"ff": ff},
+            "router": {"experts": experts, "top": top, "groups": {"count": groups, "keep": keep}}}
+
+
+def latent_spec(heads, dim, vdim, kv_rank, scale, mlp=None):
+    return {"type": "latent_attention", "mlp": mlp,
+            "mixer": {"heads": heads, "dim": dim, "vdim": vdim, "kv_rank": kv_rank, "scale": scale}}
+
+
+def gla_spec(heads, dim, vdim, tau, mlp=None):
+    return {"type": "gla", "mlp": mlp, "mixer": {"heads": heads, "dim": dim, "vdim": vdim, "tau": tau}}
+
+
+def wkv_spec(heads, dim, mlp=None):
+    return {"type": "wkv", "mlp": mlp, "mixer": {"heads": heads, "dim": dim}}
+
+
+def make_config(layers, width, vocab, loop=None, eps=1e-6, logit_scale=None):
+    cfg = {"architecture": "Nupovik", "vocab": vocab, "width": width, "norm": {"eps": eps}, "layers": layers}
+    if loop is not None:
+        cfg["loop"] = {"start": loop[0], "stop": loop[1], "times": loop[2]}
+    if logit_scale is not None:
+        cfg["logit_scale"] = logit_scale
+    return cfg
+
+
+def make_weights(cfg, seed=0, low_rank=8, slow_decay=False):
+    """A random checkpoint by tensor name, values rounded to bfloat16.  slow_decay: decays close to 1, so
+    that what the first tokens wrote into a recurrent state still counts hundreds of tokens later."""
+    g = torch.Generator().manual_seed(seed)
+    W, V = cfg["width"], cfg["vocab"]
+    w = {}
+
+    def mat(n, k, gain=1.0):
+        return torch.randn(n, k, generator=g) * gain / math.sqrt(k)
+
+    def vec(n, mean=0.0, std=0.1):
+        return mean + torch.randn(n, generator=g) * std
+
+    w["embed"], w["head"], w["final.norm"] = torch.randn(V, W, generator=g), mat(V, W), vec(W, 1.0)
+    if cfg.get("loop"):
+        w["loop.in"] = mat(W, 2 * W, math.sqrt(2.0))
+    for i, spec in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", spec["mixer"]
+        H, dk = m["heads"], m["dim"]
+        w[p + "norm1"] = vec(W, 1.0)
+        if spec["type"] == "latent_attention":
+            dv, r = m["vdim"], m["kv_rank"]
+            w.update({p + "mix.q": mat(H * dk, W), p + "mix.dkv": mat(r, W), p + "mix.dkv.norm": vec(r, 1.0),
+                      p + "mix.uk": mat(H * dk, r), p + "mix.uv": mat(H * dv, r), p + "mix.g": mat(H, W, 2.0),
+                      p + "mix.o": mat(W, H * dv)})
+        elif spec["type"] == "gla":
+            dv = m.get("vdim", dk)
+            w.update({p + "mix.q": mat(H * dk, W), p + "mix.k": mat(H * dk, W), p + "mix.v": mat(H * dv, W),
+                      p + "mix.g": mat(H * dv, W), p + "mix.o": mat(W, H * dv), p + "mix.norm": vec(dv, 1.0),
+                      p + "mix.a1": mat(low_rank, W), p + "mix.a2": mat(H * dk, low_rank),
+                      p + "mix.a2.b": vec(H * dk, 6.0 if slow_decay else 1.0, 1.0)})
+        else:
+            for s in "rkvgw":
+                w[p + "mix.mu." + s] = torch.rand(W, generator=g)
+            w.update({p + "mix.r": mat(H * dk, W), p + "mix.k": mat(H * dk, W), p + "mix.v": mat(H * dk, W),
+                      p + "mix.g": mat(H * dk, W), p + "mix.w1": mat(low_rank, W), p + "mix.w2": mat(H * dk, low_rank),
+                      p + "mix.w0": vec(H * dk, -7.0 if slow_decay else -2.0, 1.0), p + "mix.u": vec(H * dk, 0.5, 0.5).view(H, dk),
+                      p + "mix.norm": vec(H * dk, 1.0), p + "mix.o": mat(W, H * dk)})
+        mlp = spec.get("mlp")
+        if mlp is None:
+            continue
+        w[p + "norm2"] = vec(W, 1.0)
+        if mlp["kind"] == "dense":
+            w.update({p + "mlp.up": mat(mlp["ff"], W), p + "mlp.down": mat(W, mlp["ff"])})
+        else:
+            E, ff = mlp["router"]["experts"], mlp["expert"]["ff"]
+            for e in range(E):
+                w.update({f"{p}mlp.e{e}.up": mat(ff, W), f"{p}mlp.e{e}.down": mat(W, ff)})
+            w.update({p + "mlp.router": mat(E, W, 2.0), p + "mlp.correction": vec(E, 0.0, 0.5)})
+    return {k: v.to(torch.bfloat16) for k, v in w.items()}

@@ -26,10 +26,11 @@ embed_sincos_kernel(float* __restrict__ x, const T* __restrict__ table, const in
   const float p = (float)positions[row];  // exact below 2^24
   for (int64_t i = threadIdx.x; 2 * i < dim; i += kLayThreads) {
     const float a = p * freq_hi[i];
-    const float rest = fmaf(p, freq_hi[i], -a) + p * freq_lo[i];  // p f - a, to first order
-    float sn, cs;
+    const float rest = fmaf(p, freq_hi[i], -a) + p * freq_lo[i];  // p f - a: the product's rounding residue
+    float sn, cs, sr, cr;
     sincosf(a, &sn, &cs);
-    const float s2 = fmaf(rest, cs, sn), c2 = fmaf(-rest, sn, cs);  // sin(a + rest), cos(a + rest)
+    sincosf(rest, &sr, &cr);  // |rest| is a fraction of a radian even at a million positions
+    const float s2 = fmaf(sn, cr, cs * sr), c2 = fmaf(cs, cr, -sn * sr);  // sin(a + rest), cos(a + rest)
     x[row * dim + 2 * i] = to_f32<T>(table[id * dim + 2 * i]) + s2;
     if (2 * i + 1 < dim) x[row * dim + 2 * i + 1] = to_f32<T>(table[id * dim + 2 * i + 1]) + c2;
   }
