@@ -75,9 +75,10 @@ def parse_args():
     ap.add_argument("--no-roofline", action="store_true")
     ap.add_argument("--tp-steps", type=int, default=3)
     ap.add_argument("--clocks-csv", type=str, default="", help="write the nvidia-smi samples of the run here")
-    ap.add_argument("--family", type=str, default="", choices=["", "rimidra"],
+    ap.add_argument("--family", type=str, default="", choices=["", "rimidra", "nupovik"],
                     help="instead of the default workload: prefill / decode throughput and per-kernel rooflines of "
-                         "that model family beside Llama at equal size (scripts/bench_rimidra.py)")
+                         "that model family beside Llama (and, for nupovik, Rimidra) at equal size "
+                         "(scripts/bench_rimidra.py, scripts/bench_nupovik.py)")
     ap.add_argument("--family-sizes", type=str, default="s,m")
     return ap.parse_args()
 
@@ -583,8 +584,8 @@ def main():
     args = parse_args()
     if args.family:
         sys.path.insert(0, os.path.join(ROOT, "scripts"))
-        import bench_rimidra
-        res = bench_rimidra.run(tuple(args.family_sizes.split(",")))
+        import importlib
+        res = importlib.import_module("bench_" + args.family).run(tuple(args.family_sizes.split(",")))
         print(json.dumps({"family": args.family, "data": "synthetic", "dtype": "bf16", **res}))
         return
     rank = int(os.environ.get("RANK", 0))
