@@ -74,23 +74,6 @@ embed_f32_kernel(float* __restrict__ x, const T* __restrict__ table, const int64
   for (int64_t i = threadIdx.x; i < dim; i += kRowThreads) x[row * dim + i] = to_f32<T>(table[id * dim + i]);
 }
 
-// 16-byte vectors of T (8 x 16-bit or 4 x float)
-template <typename T>
-struct Vec16 {
-  static constexpr int kN = 16 / sizeof(T);
-  uint4 raw;
-  __device__ __forceinline__ T* e() { return reinterpret_cast<T*>(&raw); }
-  __device__ __forceinline__ const T* e() const { return reinterpret_cast<const T*>(&raw); }
-};
-template <typename T>
-__device__ __forceinline__ Vec16<T> ldv(const T* p) {
-  Vec16<T> v;
-  v.raw = *reinterpret_cast<const uint4*>(p);
-  return v;
-}
-template <typename T>
-__device__ __forceinline__ void stv(T* p, const Vec16<T>& v) { *reinterpret_cast<uint4*>(p) = v.raw; }
-
 // vector form: inter a multiple of the vector width, 16-byte aligned pointers
 template <typename T>
 __global__ void __launch_bounds__(kRowThreads)

@@ -59,6 +59,25 @@ __device__ __forceinline__ float act_apply(float z, int act) {
   }
 }
 
+// vector form: cols and the row stride multiples of the vector width, 16-byte aligned pointers
+template <typename T>
+__global__ void __launch_bounds__(kLayThreads)
+activation_vec_kernel(T* __restrict__ out, const T* __restrict__ x, int64_t rows, int64_t cols, int64_t x_stride,
+                      int act) {
+  griddep_wait();
+  griddep_launch_dependents();
+  constexpr int N = Vec16<T>::kN;
+  const int64_t per_row = cols / N, n = rows * per_row;
+  for (int64_t i = blockIdx.x * (int64_t)kLayThreads + threadIdx.x; i < n; i += (int64_t)gridDim.x * kLayThreads) {
+    const int64_t r = i / per_row, c = (i - r * per_row) * N;
+    const Vec16<T> v = ldv(x + r * x_stride + c);
+    Vec16<T> o;
+#pragma unroll
+    for (int k = 0; k < N; ++k) o.e()[k] = from_f32<T>(act_apply(to_f32<T>(v.e()[k]), act));
+    stv(out + r * cols + c, o);
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kLayThreads)
 activation_kernel(T* __restrict__ out, const T* __restrict__ x, int64_t rows, int64_t cols, int64_t x_stride,
@@ -102,6 +121,41 @@ rmsnorm_store_kernel(T* __restrict__ pool, T* __restrict__ out, const T* __restr
   }
 }
 
+// short rows (dim <= 32 * kWarpRowMax): one warp per row, the row in registers, eight rows per CTA
+constexpr int kWarpRowMax = 16;
+template <typename T>
+__global__ void __launch_bounds__(kLayThreads)
+rmsnorm_store_warp_kernel(T* __restrict__ pool, T* __restrict__ out, const T* __restrict__ x, const T* __restrict__ w,
+                          const int64_t* __restrict__ loc, int64_t rows, int64_t dim, int64_t x_stride,
+                          int64_t pool_stride, float eps) {
+  griddep_wait();
+  griddep_launch_dependents();
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * (kLayThreads / 32) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const T* xr = x + row * x_stride;
+  float v[kWarpRowMax];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < kWarpRowMax; ++j) {
+    const int64_t i = (int64_t)j * 32 + lane;
+    v[j] = i < dim ? to_f32<T>(xr[i]) : 0.f;
+    ss += v[j] * v[j];
+  }
+  ss = warp_sum(ss);
+  const float inv = 1.0f / sqrtf(ss / (float)dim + eps);
+  T* dst = pool != nullptr ? pool + loc[row] * pool_stride : nullptr;
+#pragma unroll
+  for (int j = 0; j < kWarpRowMax; ++j) {
+    const int64_t i = (int64_t)j * 32 + lane;
+    if (i < dim) {
+      const T y = from_f32<T>(v[j] * inv * to_f32<T>(w[i]));
+      if (dst != nullptr) dst[i] = y;
+      if (out != nullptr) out[row * dim + i] = y;
+    }
+  }
+}
+
 // out[t, h, :] = o[t, h, :] * sigmoid(g[t, h])
 template <typename T>
 __global__ void __launch_bounds__(kLayThreads)
@@ -114,6 +168,26 @@ head_gate_sigmoid_kernel(T* __restrict__ out, const T* __restrict__ o, const T* 
     const int64_t t = i / per_row, c = i - t * per_row;
     const float gate = 1.0f / (1.0f + expf(-to_f32<T>(g[t * g_stride + c / vdim])));
     out[i] = from_f32<T>(to_f32<T>(o[t * o_stride + c]) * gate);
+  }
+}
+
+// vector form: vdim and the row stride of o multiples of the vector width, 16-byte aligned pointers
+template <typename T>
+__global__ void __launch_bounds__(kLayThreads)
+head_gate_sigmoid_vec_kernel(T* __restrict__ out, const T* __restrict__ o, const T* __restrict__ g, int64_t tokens,
+                             int heads, int vdim, int64_t o_stride, int64_t g_stride) {
+  griddep_wait();
+  griddep_launch_dependents();
+  constexpr int N = Vec16<T>::kN;
+  const int64_t per_row = (int64_t)heads * vdim / N, n = tokens * per_row;
+  for (int64_t i = blockIdx.x * (int64_t)kLayThreads + threadIdx.x; i < n; i += (int64_t)gridDim.x * kLayThreads) {
+    const int64_t t = i / per_row, c = (i - t * per_row) * N;
+    const float gate = 1.0f / (1.0f + expf(-to_f32<T>(g[t * g_stride + c / vdim])));
+    const Vec16<T> v = ldv(o + t * o_stride + c);
+    Vec16<T> r;
+#pragma unroll
+    for (int k = 0; k < N; ++k) r.e()[k] = from_f32<T>(to_f32<T>(v.e()[k]) * gate);
+    stv(out + t * (int64_t)heads * vdim + c, r);
   }
 }
 
@@ -168,8 +242,14 @@ int spd_activation(void* out, const void* x, int64_t rows, int64_t cols, int64_t
               "spd_activation: bad arguments");
   if (rows == 0) return 0;
   SPD_DISPATCH_ANY(dtype, {
-    SPD_CUDA(launch(activation_kernel<T>, dim3(flat_grid(rows * cols)), dim3(kLayThreads), 0, as_stream(stream),
-                    pdl_enabled(), (T*)out, (const T*)x, rows, cols, x_stride, act));
+    constexpr int N = 16 / (int)sizeof(T);
+    if (cols % N == 0 && x_stride % N == 0 && aligned16(out) && aligned16(x)) {
+      SPD_CUDA(launch(activation_vec_kernel<T>, dim3(flat_grid(rows * cols / N)), dim3(kLayThreads), 0,
+                      as_stream(stream), pdl_enabled(), (T*)out, (const T*)x, rows, cols, x_stride, act));
+    } else {
+      SPD_CUDA(launch(activation_kernel<T>, dim3(flat_grid(rows * cols)), dim3(kLayThreads), 0, as_stream(stream),
+                      pdl_enabled(), (T*)out, (const T*)x, rows, cols, x_stride, act));
+    }
   });
   return 0;
 }
@@ -182,8 +262,15 @@ int spd_rmsnorm_store(void* pool, void* out, const void* x, const void* w, const
               "spd_rmsnorm_store: bad sizes");
   if (rows == 0) return 0;
   SPD_DISPATCH_ANY(dtype, {
-    SPD_CUDA(launch(rmsnorm_store_kernel<T>, dim3((unsigned)rows), dim3(kLayThreads), 0, as_stream(stream),
-                    pdl_enabled(), (T*)pool, (T*)out, (const T*)x, (const T*)w, loc, dim, x_stride, pool_stride, eps));
+    if (dim <= 32 * kWarpRowMax) {
+      const int64_t ctas = (rows + kLayThreads / 32 - 1) / (kLayThreads / 32);
+      SPD_CUDA(launch(rmsnorm_store_warp_kernel<T>, dim3((unsigned)ctas), dim3(kLayThreads), 0, as_stream(stream),
+                      pdl_enabled(), (T*)pool, (T*)out, (const T*)x, (const T*)w, loc, rows, dim, x_stride, pool_stride,
+                      eps));
+    } else {
+      SPD_CUDA(launch(rmsnorm_store_kernel<T>, dim3((unsigned)rows), dim3(kLayThreads), 0, as_stream(stream),
+                      pdl_enabled(), (T*)pool, (T*)out, (const T*)x, (const T*)w, loc, dim, x_stride, pool_stride, eps));
+    }
   });
   return 0;
 }
@@ -194,9 +281,16 @@ int spd_head_gate_sigmoid(void* out, const void* o, const void* g, int64_t token
   SPD_REQUIRE(tokens >= 0 && heads > 0 && vdim > 0, SPD_E_BADARG, "spd_head_gate_sigmoid: bad sizes");
   if (tokens == 0) return 0;
   SPD_DISPATCH_ANY(dtype, {
-    SPD_CUDA(launch(head_gate_sigmoid_kernel<T>, dim3(flat_grid(tokens * heads * vdim)), dim3(kLayThreads), 0,
-                    as_stream(stream), pdl_enabled(), (T*)out, (const T*)o, (const T*)g, tokens, heads, vdim, o_stride,
-                    g_stride));
+    constexpr int N = 16 / (int)sizeof(T);
+    if (vdim % N == 0 && o_stride % N == 0 && aligned16(out) && aligned16(o)) {
+      SPD_CUDA(launch(head_gate_sigmoid_vec_kernel<T>, dim3(flat_grid(tokens * heads * vdim / N)), dim3(kLayThreads), 0,
+                      as_stream(stream), pdl_enabled(), (T*)out, (const T*)o, (const T*)g, tokens, heads, vdim,
+                      o_stride, g_stride));
+    } else {
+      SPD_CUDA(launch(head_gate_sigmoid_kernel<T>, dim3(flat_grid(tokens * heads * vdim)), dim3(kLayThreads), 0,
+                      as_stream(stream), pdl_enabled(), (T*)out, (const T*)o, (const T*)g, tokens, heads, vdim,
+                      o_stride, g_stride));
+    }
   });
   return 0;
 }
