@@ -9,6 +9,7 @@
 // kernel of this mechanism.)
 #include "common.cuh"
 #include "ptx.cuh"
+#include <stdlib.h>
 
 namespace spd {
 
@@ -271,6 +272,10 @@ int attn_general_mma_try(void* out, const void* q, const void* k_pool, const voi
 // online-softmax state of the 16 rows in the accumulator layout; at the end the warps' partial
 // (max, sum, output) triples meet in shared memory, where the sink enters the denominator once.
 // Everything but the two products' operands (q, k, v, and P rounded to 16 bits) is fp32.
+// Few (request, head) pairs (small batches, one shared key/value head): the keys are split over the
+// gridDim.z CTAs of a thread-block cluster (tile i goes to warp i mod (NW gridDim.z) of the cluster);
+// each CTA merges its warps, the CTA of rank 0 then merges the CTAs' triples out of their shared
+// memory (distributed shared memory) between two cluster barriers — no workspace in global memory.
 // ------------------------------------------------------------------------------------------------
 constexpr int kGdTK = 32;        // keys per warp tile
 constexpr int kGdWarpHdr = 128;  // bytes in front of a warp's tiles: its slot numbers
@@ -323,7 +328,8 @@ attn_general_mma_decode_kernel(T* __restrict__ out, const T* __restrict__ q, con
 
   constexpr int kc = DK / 8, vc = DV / 8;  // 16-byte chunks per row; both divide 32
   const int64_t j_lo = window > 0 ? (pos - window + 1 > 0 ? pos - window + 1 : 0) : 0;
-  for (int64_t j0 = j_lo + kGdTK * warp; j0 <= pos; j0 += kGdTK * NW) {
+  const int n_split = gridDim.z;  // CTAs of the cluster that share this (request, head)
+  for (int64_t j0 = j_lo + kGdTK * ((int64_t)blockIdx.z * NW + warp); j0 <= pos; j0 += (int64_t)kGdTK * NW * n_split) {
     const int n = (int)(pos - j0 + 1 < kGdTK ? pos - j0 + 1 : kGdTK);
     __syncwarp();  // the previous tile has been read
     if (lane < n) slots[lane] = page[j0 + lane];
@@ -433,6 +439,52 @@ attn_general_mma_decode_kernel(T* __restrict__ out, const T* __restrict__ q, con
     }
   }
   __syncthreads();
+  if (n_split > 1) {
+    // this CTA's triple per row (no sink yet), then the cluster's merge by rank 0
+    float* cm = po + (size_t)NW * 16 * DV;  // [16]
+    float* cl = cm + 16;                    // [16]
+    float* co = cl + 16;                    // [16][DV]
+    for (int idx = tid; idx < R * DV; idx += NW * 32) {
+      const int row = idx / DV, c = idx - row * DV;
+      float mt = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < NW; ++w) mt = fmaxf(mt, pm[w * 16 + row]);
+      float lt = 0.f, acc = 0.f;
+#pragma unroll
+      for (int w = 0; w < NW; ++w) {
+        const float mw = pm[w * 16 + row];
+        const float f = mw == -INFINITY ? 0.f : exp2f(mw - mt);
+        lt += pl[w * 16 + row] * f;
+        acc += po[(size_t)(w * 16 + row) * DV + c] * f;
+      }
+      co[row * DV + c] = acc;
+      if (c == 0) {
+        cm[row] = mt;
+        cl[row] = lt;
+      }
+    }
+    cluster_sync_all();  // every CTA's triple is in its shared memory
+    if (blockIdx.z == 0) {
+      for (int idx = tid; idx < R * DV; idx += NW * 32) {
+        const int row = idx / DV, c = idx - row * DV;
+        const int h = g * R + row;
+        const float sink2 = sinks != nullptr ? sinks[h] * kLog2e : -INFINITY;
+        float mt = sink2;
+        for (int z = 0; z < n_split; ++z) mt = fmaxf(mt, ld_cluster_f32(map_to_rank(smem_u32(cm + row), z)));
+        float lt = sinks != nullptr ? exp2f(sink2 - mt) : 0.f;
+        float acc = 0.f;
+        for (int z = 0; z < n_split; ++z) {
+          const float mz = ld_cluster_f32(map_to_rank(smem_u32(cm + row), z));
+          const float f = mz == -INFINITY ? 0.f : exp2f(mz - mt);  // a CTA without keys adds nothing
+          lt += ld_cluster_f32(map_to_rank(smem_u32(cl + row), z)) * f;
+          acc += ld_cluster_f32(map_to_rank(smem_u32(co + row * DV + c), z)) * f;
+        }
+        out[(int64_t)r * out_stride + (int64_t)h * DV + c] = from_f32<T>(acc / lt);
+      }
+    }
+    cluster_sync_all();  // the other CTAs' shared memory stays alive until rank 0 has read it
+    return;
+  }
   for (int idx = tid; idx < R * DV; idx += NW * 32) {
     const int row = idx / DV, c = idx - row * DV;
     const int h = g * R + row;
@@ -459,7 +511,7 @@ static int gd_launch_nw(void* out, const void* q, const void* k_pool, const void
                         int64_t q_stride, int64_t out_stride, int64_t r2t_stride, float sm_scale, int window,
                         const float* sinks, const float* slopes, float qtemp_coef, int qtemp_every, cudaStream_t stream) {
   constexpr size_t tiles = (size_t)NW * (kGdWarpHdr + sizeof(T) * kGdTK * (DK + 8 + DV + 8));
-  constexpr size_t merge = sizeof(float) * NW * 16 * (DV + 2);
+  constexpr size_t merge = sizeof(float) * (NW + 1) * 16 * (DV + 2);  // the warps' triples + the CTA's own
   constexpr size_t smem = sizeof(T) * 16 * (DK + 8) + (tiles > merge ? tiles : merge);
   static bool configured = false;  // per instantiation
   if (!configured) {
@@ -467,10 +519,31 @@ static int gd_launch_nw(void* out, const void* q, const void* k_pool, const void
                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = true;
   }
-  SPD_CUDA(launch(attn_general_mma_decode_kernel<T, DK, DV, NW>, dim3((unsigned)batch, (unsigned)G), dim3(NW * 32), smem,
-                  stream, /*pdl=*/false, (T*)out, (const T*)q, (const T*)k_pool, (const T*)v_pool, req_to_token,
-                  req_pool_indices, seq_lens, H, G, q_stride, out_stride, r2t_stride, sm_scale, window, sinks, slopes,
-                  qtemp_coef, qtemp_every));
+  // split the keys over a cluster while (request, head) pairs alone leave SMs idle; a window bounds the
+  // tiles there are to share (one per warp at least)
+  int split = 1;
+  const int64_t pairs = batch * G;
+  const int sms = device_sm_count_cached();
+  const int64_t max_split = window > 0 ? (window + kGdTK * NW - 1) / (kGdTK * NW) : 8;
+  while (split * 2 <= 8 && split * 2 <= max_split && pairs * split * 2 <= sms) split *= 2;
+  static const bool no_split = getenv("SPD_ATTN_DECODE_NO_SPLIT") != nullptr;
+  if (no_split) split = 1;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3((unsigned)batch, (unsigned)G, (unsigned)split);
+  cfg.blockDim = dim3(NW * 32);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = (unsigned)split;
+  cfg.attrs = attr;
+  cfg.numAttrs = split > 1 ? 1 : 0;
+  SPD_CUDA(cudaLaunchKernelEx(&cfg, attn_general_mma_decode_kernel<T, DK, DV, NW>, (T*)out, (const T*)q,
+                              (const T*)k_pool, (const T*)v_pool, req_to_token, req_pool_indices, seq_lens, H, G,
+                              q_stride, out_stride, r2t_stride, sm_scale, window, sinks, slopes, qtemp_coef,
+                              qtemp_every));
   return 0;
 }
 

@@ -146,6 +146,62 @@ def test_grouped_routing(experts, top, groups, keep):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("heads,rank", [(5, 128), (16, 64), (3, 24), (20, 32)])
+def test_attention_over_latent_pool(dtype, heads, rank):
+    """Every query head against ONE latent row per token that serves as key and as value (one buffer): requests
+    of unequal length whose slots are interleaved in the pool, decoded in one launch and extended in portions;
+    in the long request one far key is made to win a head's softmax, so a missed key shows."""
+    from semi_pd_b200 import ops
+    dt = DT[dtype]
+    g = torch.Generator().manual_seed(heads * 100 + rank)
+    lens = [700, 129, 1, 64, 257]
+    scale = 0.25
+    total = sum(lens)
+    perm = (torch.randperm(total, generator=g) + 1).tolist()
+    pool = torch.zeros(total + 1, 1, rank, dtype=dt)
+    r2t = torch.zeros(len(lens) + 1, max(lens) + 8, dtype=torch.int32)
+    lat, qs, at = [], [], 0
+    for i, L in enumerate(lens):
+        c = torch.randn(L, rank, generator=g).to(dt)
+        q = (torch.randn(L, heads * rank, generator=g) * 0.5).to(dt)
+        if L > 600:  # head 1 of the last queries looks at key 5, far back
+            c[5] = (4.0 * c[5] / c[5].float().norm()).to(dt)
+            q[-40:, rank:2 * rank] = (8.0 * c[5].float()).to(dt)
+        slots = perm[at:at + L]
+        at += L
+        pool[slots, 0] = c
+        r2t[i, :L] = torch.tensor(slots, dtype=torch.int32)
+        lat.append(c)
+        qs.append(q)
+
+    def want(i, lo, hi):
+        c = lat[i].double()
+        q = qs[i].double()[lo:hi].view(hi - lo, heads, rank)
+        s = torch.einsum("thd,jd->thj", q, c) * scale
+        j = torch.arange(c.shape[0]).view(1, 1, -1)
+        s = s.masked_fill(j > torch.arange(lo, hi).view(-1, 1, 1), -math.inf)
+        return torch.einsum("thj,jd->thd", torch.softmax(s, -1), c).reshape(hi - lo, heads * rank)
+
+    poold, r2d = pool.to(DEV), r2t.to(DEV)
+    kw = dict(num_q_heads=heads, num_kv_heads=1, head_dim=rank, v_dim=rank, sm_scale=scale)
+    rpi = i64(list(range(len(lens))))
+    # decode: every request's last position in one launch
+    q = torch.stack([qs[i][-1] for i in range(len(lens))]).to(DEV)
+    got = ops.attn_general(q, poold, poold, r2d, rpi, seq_lens=i64(lens), **kw)
+    _close(got, torch.cat([want(i, L - 1, L) for i, L in enumerate(lens)]), dt, "decode")
+    # extend: the last n positions of every request as one ragged batch (n = 1 .. 40)
+    ns = [40, 2, 1, 17, 33]
+    q = torch.cat([qs[i][L - n:] for i, (L, n) in enumerate(zip(lens, ns))]).to(DEV)
+    starts = [sum(ns[:i]) for i in range(len(ns))]
+    got = ops.attn_general(q, poold, poold, r2d, rpi, prefix_lens=i32([L - n for L, n in zip(lens, ns)]),
+                           extend_lens=i32(ns), extend_start_loc=i32(starts), max_extend_len=max(ns), **kw)
+    ref = torch.cat([want(i, L - n, L) for i, (L, n) in enumerate(zip(lens, ns))])
+    _close(got, ref, dt, "extend")
+    far = want(0, lens[0] - 1, lens[0])[0, rank:2 * rank]
+    assert (far - lat[0][5].double()).abs().max() < 0.05 * lat[0][5].double().abs().max(), "the far key does not win"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_token_shift(dtype):
     """Portions of unequal requests, then decoding with a padded row; a slot used again starts from zeros."""
     from semi_pd_b200 import ops
