@@ -264,8 +264,8 @@ int attn_general_mma_try(void* out, const void* q, const void* k_pool, const voi
 }
 
 // ------------------------------------------------------------------------------------------------
-// Decode on the tensor cores: one CTA per (request, key/value head); the R = H / G query heads that
-// share the head are the 16 rows of the MMA's A operand (rows >= R are zero), so a K / V row leaves
+// Decode on the tensor cores: one CTA per (request, key/value head) — per 16 of its query heads where more
+// than 16 share it; the R <= 16 query heads are the 16 rows of the MMA's A operand (rows >= R are zero), so a K / V row leaves
 // the pool once per group and a tile of 32 keys costs 2 * DK / 16 + DV / 4 MMAs instead of 64 R FMAs
 // per lane.  The NW warps take the window's key tiles in turn (tile i goes to warp i mod NW); a warp
 // stages its own tile with 16-byte cp.async (rows past the end are zero-filled) and keeps the
@@ -294,8 +294,11 @@ attn_general_mma_decode_kernel(T* __restrict__ out, const T* __restrict__ q, con
   extern __shared__ __align__(16) unsigned char gd_smem[];
   T* sQ = reinterpret_cast<T*>(gd_smem);  // [16][LDK], rows >= R zero
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int r = blockIdx.x, g = blockIdx.y;
-  const int R = H / G;
+  // a group of more than 16 query heads takes several CTAs of 16 rows each (blockIdx.y = head * chunks + chunk)
+  const int chunks = (H / G + 15) / 16;
+  const int r = blockIdx.x, g = blockIdx.y / chunks;
+  const int h0 = g * (H / G) + (blockIdx.y % chunks) * 16;  // this CTA's first query head
+  const int R = H / G - (blockIdx.y % chunks) * 16 < 16 ? H / G - (blockIdx.y % chunks) * 16 : 16;
   const int64_t pos = seq_lens[r] - 1;
   if (pos < 0) return;
   unsigned char* wbase = gd_smem + kQBytes + (size_t)warp * kWarpBytes;
@@ -306,7 +309,7 @@ attn_general_mma_decode_kernel(T* __restrict__ out, const T* __restrict__ q, con
   for (int idx = tid; idx < 16 * (DK / 8); idx += NW * 32) {
     const int row = idx / (DK / 8), c = idx % (DK / 8);
     const bool ok = row < R;
-    cp_async16(smem_u32(sQ + row * LDK + c * 8), q + (int64_t)r * q_stride + ((int64_t)g * R + (ok ? row : 0)) * DK + c * 8, ok);
+    cp_async16(smem_u32(sQ + row * LDK + c * 8), q + (int64_t)r * q_stride + ((int64_t)h0 + (ok ? row : 0)) * DK + c * 8, ok);
   }
   cp_async_commit();
   cp_async_wait<0>();
@@ -318,7 +321,7 @@ attn_general_mma_decode_kernel(T* __restrict__ out, const T* __restrict__ q, con
   const float sc = sm_scale * temp * kLog2e;
   float sl[2];
 #pragma unroll
-  for (int x = 0; x < 2; ++x) sl[x] = (slopes != nullptr && rr[x] < R) ? slopes[g * R + rr[x]] * kLog2e : 0.f;
+  for (int x = 0; x < 2; ++x) sl[x] = (slopes != nullptr && rr[x] < R) ? slopes[h0 + rr[x]] * kLog2e : 0.f;
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};  // l: this thread's share of the row sum
   float o[DV / 8][4];
 #pragma unroll
@@ -467,7 +470,7 @@ attn_general_mma_decode_kernel(T* __restrict__ out, const T* __restrict__ q, con
     if (blockIdx.z == 0) {
       for (int idx = tid; idx < R * DV; idx += NW * 32) {
         const int row = idx / DV, c = idx - row * DV;
-        const int h = g * R + row;
+        const int h = h0 + row;
         const float sink2 = sinks != nullptr ? sinks[h] * kLog2e : -INFINITY;
         float mt = sink2;
         for (int z = 0; z < n_split; ++z) mt = fmaxf(mt, ld_cluster_f32(map_to_rank(smem_u32(cm + row), z)));
@@ -487,7 +490,7 @@ attn_general_mma_decode_kernel(T* __restrict__ out, const T* __restrict__ q, con
   }
   for (int idx = tid; idx < R * DV; idx += NW * 32) {
     const int row = idx / DV, c = idx - row * DV;
-    const int h = g * R + row;
+    const int h = h0 + row;
     const float sink2 = sinks != nullptr ? sinks[h] * kLog2e : -INFINITY;
     float mt = sink2;
 #pragma unroll
@@ -522,14 +525,14 @@ static int gd_launch_nw(void* out, const void* q, const void* k_pool, const void
   // split the keys over a cluster while (request, head) pairs alone leave SMs idle; a window bounds the
   // tiles there are to share (one per warp at least)
   int split = 1;
-  const int64_t pairs = batch * G;
+  const int64_t pairs = batch * G * ((H / G + 15) / 16);
   const int sms = device_sm_count_cached();
   const int64_t max_split = window > 0 ? (window + kGdTK * NW - 1) / (kGdTK * NW) : 8;
   while (split * 2 <= 8 && split * 2 <= max_split && pairs * split * 2 <= sms) split *= 2;
   static const bool no_split = getenv("SPD_ATTN_DECODE_NO_SPLIT") != nullptr;
   if (no_split) split = 1;
   cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3((unsigned)batch, (unsigned)G, (unsigned)split);
+  cfg.gridDim = dim3((unsigned)batch, (unsigned)(G * ((H / G + 15) / 16)), (unsigned)split);
   cfg.blockDim = dim3(NW * 32);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
@@ -554,7 +557,7 @@ int attn_general_mma_decode_try(void* out, const void* q, const void* k_pool, co
                                 int64_t r2t_stride, float sm_scale, int window, const float* sinks, const float* slopes,
                                 float qtemp_coef, int qtemp_every, int dtype, cudaStream_t stream) {
   if (dtype != SPD_BF16 && dtype != SPD_F16) return 1;
-  if (H / G > 16 || G > 65535 || batch >= (1ll << 31)) return 1;
+  if ((int64_t)G * ((H / G + 15) / 16) > 65535 || batch >= (1ll << 31)) return 1;
   if (q_stride % 8 != 0 || !aligned16(q) || !aligned16(k_pool) || !aligned16(v_pool)) return 1;
   // short windows do not fill eight warps: four warps then leave room for more CTAs per SM
   const bool wide = window <= 0 || window > 4 * kGdTK;
