@@ -12,8 +12,8 @@
 
 namespace spd {
 
-constexpr int kGenMaxVPerLane = 8;   // v_dim <= 256
-constexpr int kGenMaxHeadDim = 256;
+constexpr int kGenMaxVPerLane = 16;  // v_dim <= 512: value columns a lane holds (instantiated for 8 and 16)
+constexpr int kGenMaxHeadDim = 512;
 
 template <typename T>
 __device__ __forceinline__ float dot_row(const float* __restrict__ qs, const T* __restrict__ krow, int dk);
@@ -51,7 +51,7 @@ __device__ __forceinline__ float dot_row(const float* __restrict__ qs, const T* 
   return s;
 }
 
-template <typename T>
+template <typename T, int VMAX>
 __global__ void __launch_bounds__(128)
 attn_general_kernel(T* __restrict__ out, const T* __restrict__ q, const T* __restrict__ k_pool,
                     const T* __restrict__ v_pool, const int32_t* __restrict__ req_to_token,
@@ -99,9 +99,9 @@ attn_general_kernel(T* __restrict__ out, const T* __restrict__ q, const T* __res
   const float slope = slopes != nullptr ? slopes[h] : 0.f;
   float m = -INFINITY, l = 0.f;
   if (sinks != nullptr) { m = sinks[h]; l = 1.f; }
-  float acc[kGenMaxVPerLane];
+  float acc[VMAX];
 #pragma unroll
-  for (int i = 0; i < kGenMaxVPerLane; ++i) acc[i] = 0.f;
+  for (int i = 0; i < VMAX; ++i) acc[i] = 0.f;
 
   const int64_t j_lo = window > 0 ? (pos - window + 1 > 0 ? pos - window + 1 : 0) : 0;
   for (int64_t j0 = j_lo; j0 <= pos; j0 += 32) {
@@ -119,14 +119,14 @@ attn_general_kernel(T* __restrict__ out, const T* __restrict__ q, const T* __res
     l = l * corr + warp_sum(p);
     m = m_new;
 #pragma unroll
-    for (int i = 0; i < kGenMaxVPerLane; ++i) acc[i] *= corr;
+    for (int i = 0; i < VMAX; ++i) acc[i] *= corr;
     const int n = (int)(pos - j0 + 1 < 32 ? pos - j0 + 1 : 32);
     for (int jj = 0; jj < n; ++jj) {
       const float pj = __shfl_sync(0xffffffffu, p, jj);
       const int sj = __shfl_sync(0xffffffffu, slot, jj);
       const T* vrow = v_pool + ((int64_t)sj * G + g) * dv;
 #pragma unroll
-      for (int i = 0; i < kGenMaxVPerLane; ++i) {
+      for (int i = 0; i < VMAX; ++i) {
         const int c = lane + 32 * i;
         if (c < dv) acc[i] = fmaf(pj, to_f32<T>(vrow[c]), acc[i]);
       }
@@ -134,7 +134,7 @@ attn_general_kernel(T* __restrict__ out, const T* __restrict__ q, const T* __res
   }
   const float inv = 1.0f / l;
 #pragma unroll
-  for (int i = 0; i < kGenMaxVPerLane; ++i) {
+  for (int i = 0; i < VMAX; ++i) {
     const int c = lane + 32 * i;
     if (c < dv) out[t * out_stride + (int64_t)h * dv + c] = from_f32<T>(acc[i] * inv);
   }
@@ -143,7 +143,7 @@ attn_general_kernel(T* __restrict__ out, const T* __restrict__ q, const T* __res
 // Decode: one CTA per (request, query head); its four warps take the key tiles of the window in turn
 // (tile i goes to warp i mod 4) and their partial (max, sum, output) triples are merged through shared
 // memory by warp 0 — four times the loads in flight per (request, head) of the one-warp form.
-template <typename T>
+template <typename T, int VMAX>
 __global__ void __launch_bounds__(128)
 attn_general_decode_kernel(T* __restrict__ out, const T* __restrict__ q, const T* __restrict__ k_pool,
                            const T* __restrict__ v_pool, const int32_t* __restrict__ req_to_token,
@@ -169,9 +169,9 @@ attn_general_decode_kernel(T* __restrict__ out, const T* __restrict__ q, const T
   __syncthreads();
   const float slope = slopes != nullptr ? slopes[h] : 0.f;
   float m = -INFINITY, l = 0.f;
-  float acc[kGenMaxVPerLane];
+  float acc[VMAX];
 #pragma unroll
-  for (int i = 0; i < kGenMaxVPerLane; ++i) acc[i] = 0.f;
+  for (int i = 0; i < VMAX; ++i) acc[i] = 0.f;
   const int64_t j_lo = window > 0 ? (pos - window + 1 > 0 ? pos - window + 1 : 0) : 0;
   for (int64_t j0 = j_lo + 32 * warp; j0 <= pos; j0 += 128) {
     const int64_t j = j0 + lane;
@@ -188,14 +188,14 @@ attn_general_decode_kernel(T* __restrict__ out, const T* __restrict__ q, const T
     l = l * corr + warp_sum(p);
     m = m_new;
 #pragma unroll
-    for (int i = 0; i < kGenMaxVPerLane; ++i) acc[i] *= corr;
+    for (int i = 0; i < VMAX; ++i) acc[i] *= corr;
     const int n = (int)(pos - j0 + 1 < 32 ? pos - j0 + 1 : 32);
     for (int jj = 0; jj < n; ++jj) {
       const float pj = __shfl_sync(0xffffffffu, p, jj);
       const int sj = __shfl_sync(0xffffffffu, slot, jj);
       const T* vrow = v_pool + ((int64_t)sj * G + g) * dv;
 #pragma unroll
-      for (int i = 0; i < kGenMaxVPerLane; ++i) {
+      for (int i = 0; i < VMAX; ++i) {
         const int c = lane + 32 * i;
         if (c < dv) acc[i] = fmaf(pj, to_f32<T>(vrow[c]), acc[i]);
       }
@@ -203,7 +203,7 @@ attn_general_decode_kernel(T* __restrict__ out, const T* __restrict__ q, const T
   }
   if (lane == 0) { sm_m[warp] = m; sm_l[warp] = l; }
 #pragma unroll
-  for (int i = 0; i < kGenMaxVPerLane; ++i) {
+  for (int i = 0; i < VMAX; ++i) {
     const int c = lane + 32 * i;
     if (c < dv) sm_acc[warp * dv + c] = acc[i];
   }
@@ -221,7 +221,7 @@ attn_general_decode_kernel(T* __restrict__ out, const T* __restrict__ q, const T
   }
   const float inv = 1.0f / lt;
 #pragma unroll
-  for (int i = 0; i < kGenMaxVPerLane; ++i) {
+  for (int i = 0; i < VMAX; ++i) {
     const int c = lane + 32 * i;
     if (c < dv) {
       float v = 0.f;
@@ -563,7 +563,8 @@ int spd_attn_general(void* out, const void* q, const void* k_pool, const void* v
     }
     const size_t dsmem = sizeof(float) * ((size_t)head_dim + 8 + 4 * (size_t)v_dim);
     SPD_DISPATCH_ANY(dtype, {
-      SPD_CUDA(launch(attn_general_decode_kernel<T>, dim3((unsigned)batch, (unsigned)num_q_heads), dim3(128), dsmem,
+      auto kern = v_dim <= 256 ? attn_general_decode_kernel<T, 8> : attn_general_decode_kernel<T, 16>;
+      SPD_CUDA(launch(kern, dim3((unsigned)batch, (unsigned)num_q_heads), dim3(128), dsmem,
                       as_stream(stream), /*pdl=*/false, (T*)out, (const T*)q, (const T*)k_pool, (const T*)v_pool,
                       req_to_token, req_pool_indices, seq_lens, num_q_heads, num_kv_heads, head_dim, v_dim, q_stride,
                       out_stride, req_to_token_stride, sm_scale, window, sinks, slopes, qtemp_coef, qtemp_every));
@@ -582,7 +583,8 @@ int spd_attn_general(void* out, const void* q, const void* k_pool, const void* v
   SPD_REQUIRE(ctas < (1ll << 31), SPD_E_SHAPE, "spd_attn_general: batch too large");
   const size_t smem = 4 * (size_t)head_dim * sizeof(float);
   SPD_DISPATCH_ANY(dtype, {
-    SPD_CUDA(launch(attn_general_kernel<T>, dim3((unsigned)ctas), dim3(128), smem, as_stream(stream), /*pdl=*/false,
+    auto kern = v_dim <= 256 ? attn_general_kernel<T, 8> : attn_general_kernel<T, 16>;
+    SPD_CUDA(launch(kern, dim3((unsigned)ctas), dim3(128), smem, as_stream(stream), /*pdl=*/false,
                     (T*)out, (const T*)q, (const T*)k_pool, (const T*)v_pool, req_to_token, req_pool_indices, seq_lens,
                     prefix_lens, extend_lens, extend_start_loc, (int)batch, total_tokens, num_q_heads, num_kv_heads,
                     head_dim, v_dim, q_stride, out_stride, req_to_token_stride, sm_scale, window, sinks, slopes,

@@ -146,7 +146,7 @@ def test_grouped_routing(experts, top, groups, keep):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("heads,rank", [(5, 128), (16, 64), (3, 24), (20, 32), (40, 64)])
+@pytest.mark.parametrize("heads,rank", [(5, 128), (16, 64), (3, 24), (20, 32), (40, 64), (2, 320)])
 def test_attention_over_latent_pool(dtype, heads, rank):
     """Every query head against ONE latent row per token that serves as key and as value (one buffer): requests
     of unequal length whose slots are interleaved in the pool, decoded in one launch and extended in portions;
