@@ -26,20 +26,20 @@ VOCAB = BR.VOCAB
 
 
 def nupovik_config(z, moe):
-    """Eight layer runs: latent attention, three passes over (token-shift mixer, gated linear attention), one more
-    gated linear attention."""
+    """Eight layer runs: latent attention, two passes over (token-shift mixer, gated linear attention), then gated
+    linear attention, token-shift mixer, gated linear attention."""
     from semi_pd_b200.configs import _nupovik_config
     mlp = ({"kind": "moe", "expert": {"ff": z["eff"]},
             "router": {"experts": z["experts"], "top": z["top"], "groups": {"count": z["groups"], "keep": z["keep"]}}}
            if moe else {"kind": "dense", "ff": z["ff"]})
     gla = {"type": "gla", "mlp": mlp, "mixer": {"heads": z["heads"], "dim": z["dim"], "vdim": z["dim"], "tau": 16.0}}
+    wkv = {"type": "wkv", "mlp": mlp, "mixer": {"heads": z["wkv_heads"], "dim": z["wkv_dim"]}}
     layers = [
         {"type": "latent_attention", "mlp": mlp,
          "mixer": {"heads": z["heads"], "dim": z["dim"], "vdim": z["dim"], "kv_rank": z["rank"], "scale": z["dim"] ** -0.5}},
-        {"type": "wkv", "mlp": mlp, "mixer": {"heads": z["wkv_heads"], "dim": z["wkv_dim"]}},
-        gla, gla]
+        wkv, gla, gla, wkv, gla]
     cfg = {"architecture": "Nupovik", "vocab": VOCAB, "width": z["width"], "norm": {"eps": 1e-6}, "layers": layers,
-           "loop": {"start": 1, "stop": 3, "times": 4}, "logit_scale": 0.25, "context": 8192}
+           "loop": {"start": 1, "stop": 3, "times": 2}, "logit_scale": 0.25, "context": 8192}
     return _nupovik_config("nupovik-bench", cfg)
 
 
